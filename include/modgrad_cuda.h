@@ -65,6 +65,21 @@ int launch_matvec_q4k_on_stream(const uint8_t* w_q4, const float* x, float* y, i
 int launch_dequant_q4k(const uint8_t* q4k, int n_blocks, float* fp32_out);
 int launch_dequant_q4k_on_stream(const uint8_t* q4k, int n_blocks, float* fp32_out, void* stream);
 
+/* The int8-activation pair RocmGemma::qmatvec takes by default
+ * (crates/modgrad-gemma/src/rocm_gemma.rs:283, :298-305): LOSSY (about 1 %), not the parity path.
+ * launch_quantize_q8_1 replaces crates/modgrad-device/kernels/matvec_q4k_dp4a.hip:30-56 (Rust
+ * declaration rocm.rs:477): per 32 activations xq = clamp(rint(x * 127/amax), -127, 127),
+ * xd = amax/127, xsum = sum(xq) as f32; n / 32 sub-blocks (a shorter tail is ignored).
+ * launch_matvec_q4k_dp4a replaces matvec_q4k_dp4a.hip:57-116 (rocm.rs:478-479):
+ * y[row] = sum_s xd[s] * (d*sc[s]*<nibbles, xq> - dmin*m[s]*xsum[s]); a non-finite row sum is
+ * stored as 0 (matvec_q4k_dp4a.hip:104-106).  xq: 16-byte aligned for the matvec. */
+int launch_quantize_q8_1(const float* x, int8_t* xq, float* xd, float* xsum, int n);
+int launch_quantize_q8_1_on_stream(const float* x, int8_t* xq, float* xd, float* xsum, int n, void* stream);
+int launch_matvec_q4k_dp4a(const uint8_t* w, const int8_t* xq, const float* xd, const float* xsum, float* y,
+                           int out_dim, int bpr);
+int launch_matvec_q4k_dp4a_on_stream(const uint8_t* w, const int8_t* xq, const float* xd, const float* xsum,
+                                     float* y, int out_dim, int bpr, void* stream);
+
 /* y = dequant(w_q4) . x + bias, bias may be NULL.  The semantics of Op::Matvec{quant: Q4K}
  * (crates/modgrad-device/src/backend/op.rs:175-186) and of the KFD kernel's kernarg block
  * (crates/modgrad-device/src/kfd/dispatch_queue.rs:235-262); the HIP launcher has no bias. */

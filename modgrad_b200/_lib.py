@@ -30,6 +30,10 @@ SIGNATURES = {
     "launch_matvec_q4k": (ci, [vp, vp, vp, ci, ci]),
     "launch_matvec_q4k_on_stream": (ci, [vp, vp, vp, ci, ci, vp]),
     "launch_matvec_q4k_noalloc_on_stream": (ci, [vp, vp, vp, ci, ci, vp]),
+    "launch_quantize_q8_1": (ci, [vp, vp, vp, vp, ci]),
+    "launch_quantize_q8_1_on_stream": (ci, [vp, vp, vp, vp, ci, vp]),
+    "launch_matvec_q4k_dp4a": (ci, [vp, vp, vp, vp, vp, ci, ci]),
+    "launch_matvec_q4k_dp4a_on_stream": (ci, [vp, vp, vp, vp, vp, ci, ci, vp]),
     "launch_dequant_q4k": (ci, [vp, ci, vp]),
     "launch_dequant_q4k_on_stream": (ci, [vp, ci, vp, vp]),
     "mg_matvec_q4k_bias_on_stream": (ci, [vp, vp, vp, vp, ci, ci, vp]),

@@ -122,6 +122,14 @@ class DeviceBuffer:
         cuda_check(self._lib.mg_memcpy_d2h(_np_ptr(out), self.ptr, n_f32 * 4), "cudaMemcpy D2H")
         return out
 
+    def copy_to_host_bytes(self, dst: np.ndarray) -> np.ndarray:
+        """Raw bytes back to a contiguous host array (any dtype)."""
+        n = dst.nbytes
+        if n > self.bytes or not dst.flags["C_CONTIGUOUS"]:
+            raise Runtime(f"copy_to_host_bytes: dst {n} > buf {self.bytes} or not contiguous")
+        cuda_check(self._lib.mg_memcpy_d2h(_np_ptr(dst), self.ptr, n), "cudaMemcpy D2H bytes")
+        return dst
+
     def u8_at(self, offset: int) -> int:
         return self.ptr + offset
 
@@ -160,6 +168,23 @@ class kern:
         code = (L.launch_matvec_q4k(w, x, y, out_dim, bpr) if stream is None
                 else L.launch_matvec_q4k_on_stream(w, x, y, out_dim, bpr, stream))
         cuda_check(code, "matvec_q4k")
+
+    @staticmethod
+    def quantize_q8_1(x: int, xq: int, xd: int, xsum: int, n: int, stream: int | None = None) -> None:
+        """``kern::quantize_q8_1`` (rocm.rs:971): f32 x -> int8 + per-32 scale + per-32 sum."""
+        L = _lib.load()
+        code = (L.launch_quantize_q8_1(x, xq, xd, xsum, n) if stream is None
+                else L.launch_quantize_q8_1_on_stream(x, xq, xd, xsum, n, stream))
+        cuda_check(code, "quantize_q8_1")
+
+    @staticmethod
+    def matvec_q4k_dp4a(w: int, xq: int, xd: int, xsum: int, y: int, out_dim: int, bpr: int,
+                        stream: int | None = None) -> None:
+        """``kern::matvec_q4k_dp4a`` (rocm.rs:973-975): the lossy int8-activation matvec."""
+        L = _lib.load()
+        code = (L.launch_matvec_q4k_dp4a(w, xq, xd, xsum, y, out_dim, bpr) if stream is None
+                else L.launch_matvec_q4k_dp4a_on_stream(w, xq, xd, xsum, y, out_dim, bpr, stream))
+        cuda_check(code, "matvec_q4k_dp4a")
 
     @staticmethod
     def dequant_q4k(q4k: int, n_blocks: int, out: int, stream: int | None = None) -> None:

@@ -337,11 +337,13 @@ int mg_sdpa_decode_f16kv_on_stream(const float* q, const void* k_cache, const vo
                                    int n_heads, int n_kv_heads, int head_dim, int seq_len,
                                    const int* seq_len_dev, float scale, void* scratch, int n_splits,
                                    void* stream) {
+    const mgpeer::PeerSync peer = mgpeer::take_next_peer_sync();  // consumed on every path, errors included
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_splits <= 0 || n_splits > kMaxSplits)
         return (int)cudaErrorInvalidValue;
     if (head_dim != 64 && head_dim != 128 && head_dim != 256) return (int)cudaErrorInvalidValue;
     if (!seq_len_dev && seq_len <= 0) return (int)cudaErrorInvalidValue;
     if (!q || !k_cache || !v_cache || !out || !scratch) return (int)cudaErrorInvalidValue;
+    if (peer.world > 1 && !mgpeer::in_arena(peer, out, (size_t)n_heads * head_dim * sizeof(float))) return (int)cudaErrorInvalidValue;
     const int grp = n_heads / n_kv_heads, kv_dim = n_kv_heads * head_dim;
     const dim3 grid((unsigned)n_kv_heads, (unsigned)n_splits);
     cudaStream_t s = (cudaStream_t)stream;
@@ -354,7 +356,7 @@ int mg_sdpa_decode_f16kv_on_stream(const float* q, const void* k_cache, const vo
     else e = launch_split<2>(grp, grid, s, q, k, v, part, seq_len_dev, seq_len, n_kv_heads, kv_dim, scale, n_splits);
     if (e != cudaSuccess) return (int)e;
     return (int)mg::launch_pdl(sdpa_merge_kernel, dim3((unsigned)n_heads), dim3(128), 0, s, (const float*)part, out,
-                               head_dim, n_splits, mg::early_trigger_flag() ? 0 : 1, mgpeer::take_next_peer_sync());
+                               head_dim, n_splits, mg::early_trigger_flag() ? 0 : 1, peer);
 }
 
 // freq_table (device, head_dim/2 floats, may be null): base^(-2i/head_dim) precomputed by the

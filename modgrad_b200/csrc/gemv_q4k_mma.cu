@@ -1,0 +1,516 @@
+// Batch-1 Q4_K matvec on the integer tensor-core path: y[row] = sum_e dequant(W)[row][e] * x[e] (+ addend).
+//
+// The GEMV is HBM-bound (0.5625 bytes per weight) but its instruction count decides whether a
+// launch reaches the memory rate: with dp4a every weight costs about two lane-operations.  Here
+// the dot products go to `mma.sync.m16n8k32` (u8 x s8 -> s32) and the lanes only mask nibbles and
+// apply the 6-bit scales, a little over one lane-operation per weight, so eight warps keep up
+// with the memory system and a CTA needs half an SM.  Two CTAs of consecutive launches are then
+// resident together: under programmatic dependent launch the successor's weight stream is
+// already in shared memory when its predecessor retires.
+//
+// Arithmetic (per 256-weight super-block b and row r; the format is q4k_device.cuh):
+//   x is rewritten once per CTA as 23-bit integers a_e with ONE power-of-two scale s_b per
+//   super-block, x_e ~= s_b * a_e, |a_e| <= 2^22, and each a_e as three balanced signed byte limbs
+//   a = a2*65536 + a1*256 + a0 (a1, a0 in [-128, 127]).  The rounding error per element is at most
+//   2^-22 of the largest magnitude of its super-block.  For a 16-row tile and a 64-byte pair of
+//   quant groups two chained MMAs give, per row, the exact integer sums  S[sub][limb] = sum q*a_limb
+//   of two sub-blocks at once (the k = 32 slots of an MMA are 16 bytes of either group, the
+//   activation operand holds the limbs of one group in columns 0..2 and of the other in 3..5,
+//   zero elsewhere).  Lanes fold the 6-bit scales in integer arithmetic, acc[limb] += sc * S, and
+//   once per super-block  y += d * s_b * (65536*acc2 + 256*acc1 + acc0).  High nibbles are used
+//   in place as 16*q.  The min term  -dmin * s_b * sum_sub m[sub] * sum(a)[sub]  is one more MMA
+//   whose weight operand is the unpacked 6-bit mins and whose activation operand holds four byte
+//   limbs of the eight sub-block sums.
+//
+// Pipeline: a CTA owns 16-row tiles (tile = blockIdx.x + i * gridDim.x).  A manager warp streams
+// them into a ring of shared-memory stages with one cp.async.bulk per row (rows padded to a
+// stride of 64 mod 128 bytes: conflict-free 16-byte reads), completion on an mbarrier per
+// stage.  The eight consumer warps split the super-blocks of a stage round-robin, keep per-row
+// partial sums in registers, and after the last window of a tile leave them in shared memory;
+// their arrival on the stage's second mbarrier tells the manager that the stage can be refilled
+// and that the partials can be summed (fixed order: results are deterministic) and stored.
+// Every wait is bounded; a wait that runs out is counted and the CTA drains and returns.
+//
+// The first copies are issued BEFORE the kernel waits for its predecessor in the stream
+// (griddepcontrol.wait): weights must not be produced by the kernel launched just before a
+// matvec on the same stream.
+#include "gemv_q4k_mma.hpp"
+
+#include <float.h>
+
+#include "gemv_q4k_device.cuh"
+#include "launch_common.cuh"
+#include "q4k_device.cuh"
+
+namespace gemvmma {
+
+using gemvdev::bulk_copy_g2s;
+using gemvdev::griddep_launch_dependents;
+using gemvdev::griddep_wait;
+using gemvdev::mbar_arrive_expect_tx;
+using gemvdev::mbar_init;
+using gemvdev::mbar_try_wait;
+using gemvdev::smem_u32;
+
+constexpr int kConsumerWarps = 8;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kTileRows = 16;
+constexpr int kMaxDepth = 6;
+constexpr int kXBlockBytes = 816;  // per super-block: 768 B limb fragments, 32 B sum fragments, scale, pad
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+struct Params {
+    const uint8_t* w;
+    const float* x;
+    const float* addend;  // may be null; may alias y
+    float* y;
+    int rows, bpr;
+    int n_win, kb;      // windows per tile, super-blocks per window (the last may be shorter)
+    int depth;          // stages in the ring
+    int row_stride;     // bytes between the rows of a stage
+    int x_aligned, hold_trigger;
+    unsigned* timeouts;
+};
+
+__host__ __device__ inline int round128(int v) { return (v + 127) & ~127; }
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mma_u8s8(int& c0, int& c1, int& c2, int& c3, uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c0), "+r"(c1), "+r"(c2), "+r"(c3)
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Bounded wait on an mbarrier phase; false when it ran out or another warp of the CTA gave up.
+__device__ __forceinline__ bool wait_phase(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if (++spins > kSpinLimit || *abort_flag) return false;
+    }
+    return true;
+}
+
+// ---------------------------------------------------------------------------------------------
+// x -> per-super-block operand table.  One warp converts one super-block; lane l owns elements
+// 8l .. 8l+7 (a quarter of sub-block l/4).
+//
+// Table of one super-block (816 bytes):
+//   [ (p*2+h)*12 + idx ] x 16 bytes, p = pair of quant groups (0,1), h = nibble plane (0 low, 1 high):
+//       the activation fragments of the two chained MMAs of (p, h) for the lane that holds column
+//       n of slot group t:  idx = n*2 + t for n < 3, t < 2 (limbs of group 2p) and
+//       6 + (n-3)*2 + (t-2) for 3 <= n < 6, t >= 2 (limbs of group 2p+1); bytes 0..7 = registers
+//       b0, b1 of the first MMA, 8..15 of the second.  Slot (t, half, i) of MMA j is quant byte
+//       16t + 8j + 4*half + i of the 64-byte pair.
+//   768 + (n*2 + t)*4 + i : limb n (most significant first) of the integer sum of sub-block 4t + i
+//   800 : f32 scale s_b / 16 (NaN when the super-block holds a non-finite activation)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void load8(float (&v)[8], const float* p, int aligned) {
+    if (aligned) {
+        const float4 a = *reinterpret_cast<const float4*>(p);
+        const float4 b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = p[i];
+    }
+}
+
+__device__ __forceinline__ void convert_block(const float (&v)[8], uint8_t* xb, int lane) {
+    float amax = 0.f;
+    int bad = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float a = fabsf(v[i]);
+        bad |= !(a <= FLT_MAX);  // inf or NaN
+        amax = fmaxf(amax, a);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, o);
+    }
+    int E = (int)(__float_as_uint(amax) >> 23) - 127;  // floor(log2(amax)); -127 for 0 / sub-normal
+    E = max(E, -100);
+    const float inv = __uint_as_float((uint32_t)(21 - E + 127) << 23);  // 2^(21-E)
+    uint32_t lo[3] = {0, 0, 0}, hi[3] = {0, 0, 0};
+    int sum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int a = bad ? 0 : __float2int_rn(v[i] * inv);  // |a| <= 2^22
+        sum += a;
+        const int l0 = (a << 24) >> 24;  // balanced digits
+        const int r1 = (a - l0) >> 8;
+        const int l1 = (r1 << 24) >> 24;
+        const int l2 = (r1 - l1) >> 8;
+        const int sh = 8 * (i & 3);
+        uint32_t* dst = i < 4 ? lo : hi;
+        dst[0] |= ((uint32_t)l2 & 0xFFu) << sh;
+        dst[1] |= ((uint32_t)l1 & 0xFFu) << sh;
+        dst[2] |= ((uint32_t)l0 & 0xFFu) << sh;
+    }
+    const int sub = lane >> 2, G = sub >> 1, h = sub & 1, p = G >> 1;
+    const int tlow = (lane & 3) >> 1, j = lane & 1;
+#pragma unroll
+    for (int n = 0; n < 3; ++n) {
+        const int idx = (G & 1) * 6 + n * 2 + tlow;
+        *reinterpret_cast<uint2*>(xb + ((p * 2 + h) * 12 + idx) * 16 + j * 8) = make_uint2(lo[n], hi[n]);
+    }
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    if ((lane & 3) == 0) {  // |sum| <= 2^27: four balanced limbs
+        const int l3 = (sum << 24) >> 24;
+        const int r1 = (sum - l3) >> 8;
+        const int l2 = (r1 << 24) >> 24;
+        const int r2 = (r1 - l2) >> 8;
+        const int l1 = (r2 << 24) >> 24;
+        const int l0 = (r2 - l1) >> 8;
+        uint8_t* s = xb + 768 + (sub >> 2) * 4 + (sub & 3);
+        s[0] = (uint8_t)l0;
+        s[8] = (uint8_t)l1;
+        s[16] = (uint8_t)l2;
+        s[24] = (uint8_t)l3;
+    }
+    if (lane == 0) {
+        // A non-finite activation poisons its super-block: every row's sum becomes NaN, as it
+        // does in the reference (w * NaN).
+        const float s16 = __uint_as_float((uint32_t)(E - 25 + 127) << 23);  // 2^(E-21) / 16
+        *reinterpret_cast<float*>(xb + 800) = bad ? __uint_as_float(0x7FC00000u) : s16;
+    }
+}
+
+// Per-lane constants of the MMA fragment layout (g = lane / 4 is the row / column group,
+// t = lane % 4 the slot group).
+struct LaneConst {
+    int g, t;
+    int b_active, b_off;  // activation fragment of the limb MMAs: byte offset inside a (p, h) group
+    int s_active, s_off;  // activation fragment of the min-term MMA
+    uint32_t sel0, sel1;  // byte_perm selectors of the scale for accumulator columns 2t and 2t+1
+    float w0, w1;         // limb weights of those columns
+    float v0, v1;         // limb weights of the sum columns
+};
+
+__device__ __forceinline__ LaneConst lane_const(int lane) {
+    LaneConst c;
+    c.g = lane >> 2;
+    c.t = lane & 3;
+    const int n = c.g;
+    c.b_active = (n < 3 && c.t < 2) || (n >= 3 && n < 6 && c.t >= 2);
+    c.b_off = (n < 3 ? n * 2 + c.t : 6 + (n - 3) * 2 + (c.t - 2)) * 16;
+    c.s_active = n < 4 && c.t < 2;
+    c.s_off = 768 + (n * 2 + c.t) * 4;
+    // columns 0..2: limbs of the pair's first group, 3..5: of its second group
+    c.sel0 = 0x4440u + (c.t >= 2 ? 2u : 0u);
+    c.sel1 = 0x4440u + (c.t >= 1 ? 2u : 0u);
+    c.w0 = c.t == 0 ? 65536.f : (c.t == 1 ? 1.f : (c.t == 2 ? 256.f : 0.f));
+    c.w1 = c.t == 0 ? 256.f : (c.t == 1 ? 65536.f : (c.t == 2 ? 1.f : 0.f));
+    c.v0 = c.t == 0 ? 16777216.f : (c.t == 1 ? 256.f : 0.f);
+    c.v1 = c.t == 0 ? 65536.f : (c.t == 1 ? 1.f : 0.f);
+    return c;
+}
+
+// One super-block of a 16-row tile: blk = the block's bytes of row 0 inside the stage, xb = the
+// block's operand table.  racc0 / racc1 accumulate rows g and g + 8 (partial over this lane's columns).
+__device__ __forceinline__ void process_block(const uint8_t* blk, int row_stride, const uint8_t* xb,
+                                              const LaneConst& lc, float& racc0, float& racc1) {
+    const uint8_t* r0p = blk + lc.g * row_stride;
+    const uint8_t* r1p = r0p + 8 * row_stride;
+    const uint4 h0 = *reinterpret_cast<const uint4*>(r0p);
+    const uint4 h1 = *reinterpret_cast<const uint4*>(r1p);
+    const float2 dd0 = __half22float2(*reinterpret_cast<const __half2*>(&h0.x));
+    const float2 dd1 = __half22float2(*reinterpret_cast<const __half2*>(&h1.x));
+    const float d0 = fabsf(dd0.x) <= 65504.0f ? dd0.x : 0.0f;  // inf / NaN -> 0
+    const float m0 = fabsf(dd0.y) <= 65504.0f ? dd0.y : 0.0f;
+    const float d1 = fabsf(dd1.x) <= 65504.0f ? dd1.x : 0.0f;
+    const float m1 = fabsf(dd1.y) <= 65504.0f ? dd1.y : 0.0f;
+    const q4k::ScaleMin s0 = q4k::unpack_scales(h0.y, h0.z, h0.w);
+    const q4k::ScaleMin s1 = q4k::unpack_scales(h1.y, h1.z, h1.w);
+    const float s_b = *reinterpret_cast<const float*>(xb + 800);
+
+    // min term: sum_sub m[sub] * sum(a)[sub], limbs of the sums in columns 0..3
+    int cm0 = 0, cm1 = 0, cm2 = 0, cm3 = 0;
+    {
+        const uint32_t am0 = lc.t == 0 ? s0.m_lo : (lc.t == 1 ? s0.m_hi : 0u);
+        const uint32_t am1 = lc.t == 0 ? s1.m_lo : (lc.t == 1 ? s1.m_hi : 0u);
+        uint32_t bm = 0;
+        if (lc.s_active) bm = *reinterpret_cast<const uint32_t*>(xb + lc.s_off);
+        mma_u8s8(cm0, cm1, cm2, cm3, am0, am1, 0u, 0u, bm, 0u);
+    }
+    int lo00 = 0, lo01 = 0, lo10 = 0, lo11 = 0, hi00 = 0, hi01 = 0, hi10 = 0, hi11 = 0;
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+        const uint4 q0 = *reinterpret_cast<const uint4*>(r0p + 16 + p * 64 + lc.t * 16);
+        const uint4 q1 = *reinterpret_cast<const uint4*>(r1p + 16 + p * 64 + lc.t * 16);
+        const uint32_t scw0 = p ? s0.sc_hi : s0.sc_lo;
+        const uint32_t scw1 = p ? s1.sc_hi : s1.sc_lo;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint4 bf = make_uint4(0u, 0u, 0u, 0u);
+            if (lc.b_active) bf = *reinterpret_cast<const uint4*>(xb + (p * 2 + h) * 192 + lc.b_off);
+            const uint32_t mask = h ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
+            int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+            mma_u8s8(c0, c1, c2, c3, q0.x & mask, q1.x & mask, q0.y & mask, q1.y & mask, bf.x, bf.y);
+            mma_u8s8(c0, c1, c2, c3, q0.z & mask, q1.z & mask, q0.w & mask, q1.w & mask, bf.z, bf.w);
+            const int sc00 = (int)__byte_perm(scw0, 0u, lc.sel0 + h), sc01 = (int)__byte_perm(scw0, 0u, lc.sel1 + h);
+            const int sc10 = (int)__byte_perm(scw1, 0u, lc.sel0 + h), sc11 = (int)__byte_perm(scw1, 0u, lc.sel1 + h);
+            if (h == 0) {
+                lo00 += sc00 * c0; lo01 += sc01 * c1; lo10 += sc10 * c2; lo11 += sc11 * c3;
+            } else {
+                hi00 += sc00 * c0; hi01 += sc01 * c1; hi10 += sc10 * c2; hi11 += sc11 * c3;
+            }
+        }
+    }
+    // |lo| <= 4*63*15*128*32 < 2^24, |hi| <= 16 times that: lo*16 + hi < 2^29, exact
+    const float k00 = (float)(lo00 * 16 + hi00), k01 = (float)(lo01 * 16 + hi01);
+    const float k10 = (float)(lo10 * 16 + hi10), k11 = (float)(lo11 * 16 + hi11);
+    const float v0 = fmaf(lc.w0, k00, lc.w1 * k01);
+    const float v1 = fmaf(lc.w0, k10, lc.w1 * k11);
+    const float n0 = fmaf(lc.v0, (float)cm0, lc.v1 * (float)cm1);
+    const float n1 = fmaf(lc.v0, (float)cm2, lc.v1 * (float)cm3);
+    racc0 = fmaf(d0 * s_b, v0, racc0);
+    racc0 = fmaf(-(m0 * s_b) * 16.0f, n0, racc0);
+    racc1 = fmaf(d1 * s_b, v1, racc1);
+    racc1 = fmaf(-(m1 * s_b) * 16.0f, n1, racc1);
+}
+
+__global__ void __launch_bounds__(kThreads, 2) matvec_q4k_mma_kernel(const Params p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full_bar[kMaxDepth];
+    __shared__ __align__(8) uint64_t done_bar[kMaxDepth];
+    __shared__ int abort_word;
+    volatile int* abort_flag = &abort_word;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int depth = p.depth;
+    const int stage_bytes = kTileRows * p.row_stride;
+    uint8_t* xtab = smem;
+    float* partials = reinterpret_cast<float*>(smem + round128(p.bpr * kXBlockBytes));  // [depth+1][8][16]
+    uint8_t* stages = reinterpret_cast<uint8_t*>(partials) + round128((depth + 1) * kConsumerWarps * kTileRows * 4);
+    const size_t row_bytes = (size_t)p.bpr * q4k::kBlockBytes;
+    const int n_tiles = (p.rows + kTileRows - 1) / kTileRows;
+    const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int total = my_tiles * p.n_win;  // stage uses of this CTA
+
+    if (!p.hold_trigger) griddep_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < depth; ++s) {
+            mbar_init(full_bar + s, 1);
+            mbar_init(done_bar + s, kConsumerWarps);
+        }
+        abort_word = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // Fills the stage of use `u` (tile u / n_win, window u % n_win); all lanes of the manager warp call it.
+    auto issue = [&](int u) {
+        const int ti = u / p.n_win, win = u - ti * p.n_win;
+        const int row0 = ((int)blockIdx.x + ti * (int)gridDim.x) * kTileRows;
+        const int valid = min(kTileRows, p.rows - row0);
+        const int b0 = win * p.kb;
+        const uint32_t bytes = (uint32_t)(min(p.kb, p.bpr - b0) * q4k::kBlockBytes);
+        const int s = u % depth;
+        if (lane == 0) mbar_arrive_expect_tx(full_bar + s, bytes * (uint32_t)valid);
+        __syncwarp();
+        if (lane < valid)
+            bulk_copy_g2s(stages + (size_t)s * stage_bytes + lane * p.row_stride,
+                          p.w + (size_t)(row0 + lane) * row_bytes + (size_t)b0 * q4k::kBlockBytes, bytes, full_bar + s);
+    };
+
+    int issued = 0;
+    if (warp == kConsumerWarps) {  // weights do not depend on the previous kernel
+        for (; issued < depth && issued < total; ++issued) issue(issued);
+    }
+
+    griddep_wait();  // x may be produced by the kernel launched just before this one
+
+    {   // every warp converts super-blocks warp, warp + 9, ...; loads of four blocks in flight at once
+        constexpr int kU = 4;
+        constexpr int kWarps = kConsumerWarps + 1;
+        for (int b0 = warp; b0 < p.bpr; b0 += kWarps * kU) {
+            float v[kU][8];
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+                const int b = b0 + u * kWarps;
+                if (b < p.bpr) load8(v[u], p.x + (size_t)b * 256 + lane * 8, p.x_aligned);
+            }
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+                const int b = b0 + u * kWarps;
+                if (b < p.bpr) convert_block(v[u], xtab + (size_t)b * kXBlockBytes, lane);
+            }
+        }
+    }
+    __syncthreads();
+
+    if (warp == kConsumerWarps) {
+        // ---- manager: refill stages as they are released, finish tiles -------------------------
+        int ti = 0, win = 0, u = 0;
+        bool ok = true;
+        for (; u < total; ++u) {
+            const int s = u % depth;
+            if (!wait_phase(done_bar + s, (uint32_t)(u / depth) & 1u, abort_flag)) {
+                ok = false;
+                break;
+            }
+            if (issued < total) issue(issued++);
+            if (win == p.n_win - 1) {
+                if (lane < kTileRows) {
+                    const int row = ((int)blockIdx.x + ti * (int)gridDim.x) * kTileRows + lane;
+                    if (row < p.rows) {
+                        const float* pp = partials + (size_t)(ti % (depth + 1)) * kConsumerWarps * kTileRows + lane;
+                        float sum = 0.0f;
+#pragma unroll
+                        for (int w = 0; w < kConsumerWarps; ++w) sum += pp[w * kTileRows];
+                        if (p.addend != nullptr) sum += p.addend[row];
+                        p.y[row] = sum;
+                    }
+                }
+                win = 0;
+                ++ti;
+            } else {
+                ++win;
+            }
+        }
+        if (!ok) {
+            // Never expected.  Report, stop the consumers, and let the copies still in flight land
+            // before the CTA (and its shared memory) goes away.
+            if (lane == 0) {
+                atomicAdd(p.timeouts, 1u);
+                *abort_flag = 1;
+            }
+            __syncwarp();
+            for (int v = u; v < issued; ++v) {
+                uint32_t spins = 0;
+                while (!mbar_try_wait(full_bar + v % depth, (uint32_t)(v / depth) & 1u) && ++spins < kSpinLimit) {
+                }
+            }
+        }
+    } else {
+        // ---- consumers ---------------------------------------------------------------------------
+        const LaneConst lc = lane_const(lane);
+        float racc0 = 0.0f, racc1 = 0.0f;
+        int ti = 0, win = 0, blk_seq = 0;
+        for (int u = 0; u < total; ++u) {
+            const int s = u % depth;
+            if (!wait_phase(full_bar + s, (uint32_t)(u / depth) & 1u, abort_flag)) {
+                if (lane == 0) {
+                    atomicAdd(p.timeouts, 1u);
+                    *abort_flag = 1;
+                }
+                break;
+            }
+            const int b0 = win * p.kb;
+            const int nb = min(p.kb, p.bpr - b0);
+            const uint8_t* stage = stages + (size_t)s * stage_bytes;
+            for (int i = (warp - blk_seq) & 7; i < nb; i += kConsumerWarps)
+                process_block(stage + i * q4k::kBlockBytes, p.row_stride, xtab + (size_t)(b0 + i) * kXBlockBytes, lc,
+                              racc0, racc1);
+            blk_seq = (blk_seq + nb) & 7;
+            if (win == p.n_win - 1) {
+                racc0 += __shfl_xor_sync(0xFFFFFFFFu, racc0, 1);
+                racc0 += __shfl_xor_sync(0xFFFFFFFFu, racc0, 2);
+                racc1 += __shfl_xor_sync(0xFFFFFFFFu, racc1, 1);
+                racc1 += __shfl_xor_sync(0xFFFFFFFFu, racc1, 2);
+                if (lc.t == 0) {
+                    float* pp = partials + ((size_t)(ti % (depth + 1)) * kConsumerWarps + warp) * kTileRows;
+                    pp[lc.g] = racc0;
+                    pp[lc.g + 8] = racc1;
+                }
+                racc0 = racc1 = 0.0f;
+                win = 0;
+                ++ti;
+            } else {
+                ++win;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(done_bar + s);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kSmemTwoPerSm = 115456;  // two CTAs per SM: 2 x (this + static + 1 KiB reserved) <= 228 KiB
+constexpr int kSmemOnePerSm = 226 * 1024;
+
+int pad_row_stride(int bytes) {  // next multiple of 16 that is 64 mod 128
+    int s = (bytes + 15) & ~15;
+    while ((s & 127) != 64) s += 16;
+    return s;
+}
+
+struct Config {
+    int n_win = 0, kb = 0, depth = 0, row_stride = 0, smem = 0;
+};
+
+// The ring that keeps the most weight bytes in flight inside `budget` bytes of shared memory.
+bool pick_config(int bpr, int budget, Config& best) {
+    const int xtab = round128(bpr * kXBlockBytes);
+    long best_flight = -1;
+    for (int n_win = 1; n_win <= bpr; ++n_win) {
+        const int kb = (bpr + n_win - 1) / n_win;
+        if ((bpr + kb - 1) / kb != n_win) continue;  // same windows as a smaller n_win
+        const int row_stride = pad_row_stride(kb * q4k::kBlockBytes);
+        const int stage = kTileRows * row_stride;
+        for (int depth = kMaxDepth; depth >= 3; --depth) {
+            const int smem = xtab + round128((depth + 1) * kConsumerWarps * kTileRows * 4) + depth * stage;
+            if (smem > budget) continue;
+            const long flight = (long)(depth - 1) * kTileRows * kb * q4k::kBlockBytes;
+            if (flight > best_flight) {
+                best_flight = flight;
+                best = Config{n_win, kb, depth, row_stride, smem};
+            }
+            break;
+        }
+    }
+    return best_flight >= 0;
+}
+
+}  // namespace
+
+bool supported(int blocks_per_row) {
+    Config c;
+    return blocks_per_row > 0 && pick_config(blocks_per_row, kSmemOnePerSm, c);
+}
+
+cudaError_t launch(const uint8_t* w, const float* x, const float* addend, float* y, int rows, int bpr,
+                   int hold_trigger, unsigned* timeouts, int sms, cudaStream_t stream) {
+    Config c;
+    // Half an SM when a useful ring fits beside the operand table (the successor kernel can then be
+    // resident early); the whole SM for long rows.
+    const bool two = pick_config(bpr, kSmemTwoPerSm, c) &&
+                     (long)(c.depth - 1) * kTileRows * c.kb * q4k::kBlockBytes >= 48 * 1024;
+    if (!two && !pick_config(bpr, kSmemOnePerSm, c)) return cudaErrorInvalidValue;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(matvec_q4k_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSmemOnePerSm);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(matvec_q4k_mma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 (int)cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    Params p = {};
+    p.w = w; p.x = x; p.addend = addend; p.y = y;
+    p.rows = rows; p.bpr = bpr;
+    p.n_win = c.n_win; p.kb = c.kb; p.depth = c.depth; p.row_stride = c.row_stride;
+    p.x_aligned = mg::aligned16(x) ? 1 : 0;
+    p.hold_trigger = hold_trigger;
+    p.timeouts = timeouts;
+    const int n_tiles = (rows + kTileRows - 1) / kTileRows;
+    const int grid = n_tiles < sms ? n_tiles : sms;
+    return mg::launch_pdl(matvec_q4k_mma_kernel, dim3((unsigned)grid), dim3(kThreads), (size_t)c.smem, stream, p);
+}
+
+}  // namespace gemvmma

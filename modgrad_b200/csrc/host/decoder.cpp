@@ -353,7 +353,7 @@ int setup_peer_exchange(mg_decoder* d) {
         for (int r = 0; r < world; ++r) all = all && host[r].ok;
         if (pass == 0) {
             int opened = all ? 1 : 0;
-            d->px.rank = d->rank; d->px.world = world;
+            d->px.rank = d->rank; d->px.world = world; d->px.bytes = d->arena_bytes;
             for (int r = 0; r < world && opened; ++r) {
                 if (r == d->rank) { d->px.base[r] = d->arena; continue; }
                 void* p = nullptr;

@@ -36,6 +36,7 @@
 #include <mutex>
 
 #include "gemv_q4k_device.cuh"
+#include "gemv_q4k_mma.hpp"
 #include "launch_common.cuh"
 #include "q4k_device.cuh"
 #include "xlimbs.cuh"
@@ -332,6 +333,13 @@ cudaError_t workspace_for(cudaStream_t stream, size_t bytes, void** out) {
 // conversion kernel plus a scratch table.
 constexpr int kFusedConvertMaxBpr = 32;
 
+// An armed exchange stores the output at the same offset of every peer's arena: the target must
+// lie inside this rank's arena, behind the flag block.
+bool peer_target_ok(const mgpeer::PeerSync& ps, const void* out, size_t bytes) {
+    if (ps.world <= 1) return true;
+    return mgpeer::in_arena(ps, out, bytes);
+}
+
 bool limbs_path_ok(int bpr) { return xlimbs::record_bytes((size_t)bpr * 256) <= (size_t)kMaxRecordSmem; }
 
 }  // namespace
@@ -361,8 +369,10 @@ extern "C" int mg_q4k_x_to_limbs_on_stream(const float* x, int k, void* records,
 // projection, produced directly in limb form.
 extern "C" int mg_swiglu_limbs_on_stream(const float* gate, const float* up, float* act_out, int n,
                                          void* records, void* stream) {
+    const mgpeer::PeerSync peer = mgpeer::take_next_peer_sync();  // consumed on every path, errors included
     if (!gate || !up || !records || n <= 0 || (n % 64) != 0) return (int)cudaErrorInvalidValue;
     if (!mg::aligned16(records)) return (int)cudaErrorInvalidValue;
+    if (!peer_target_ok(peer, records, xlimbs::record_bytes((size_t)n))) return (int)cudaErrorInvalidValue;
     const int threads = n / 4;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
@@ -375,7 +385,7 @@ extern "C" int mg_swiglu_limbs_on_stream(const float* gate, const float* up, flo
     cfg.numAttrs = 1;
     const int aligned = (mg::aligned16(gate) && mg::aligned16(up)) ? 1 : 0;
     return (int)cudaLaunchKernelEx(&cfg, x_to_limbs_kernel, gate, up, act_out, static_cast<uint32_t*>(records),
-                                   threads, aligned, mg::early_trigger_flag() ? 0 : 1, mgpeer::take_next_peer_sync());
+                                   threads, aligned, mg::early_trigger_flag() ? 0 : 1, peer);
 }
 
 // Number of warps of the GEMV that ever gave up waiting for a weight copy on the current
@@ -388,11 +398,14 @@ extern "C" long long mg_matvec_q4k_timeouts(void) {
 
 extern "C" size_t mg_q4k_limb_record_bytes(int k) { return k > 0 ? xlimbs::record_bytes((size_t)k) : 0; }
 
+// `peer`: the exchange armed for this launch by an engine that wants the output all-gathered
+// (taken from the host thread's slot by the extern "C" entry point, whatever path it then takes).
 template <int FROM_X>
-int dispatch_multi(const MatList& ml_in, const void* src, int blocks_per_row, cudaStream_t s) {
+int dispatch_multi(const MatList& ml_in, const void* src, int blocks_per_row, const mgpeer::PeerSync& peer,
+                   cudaStream_t s) {
     MatList ml = ml_in;
     ml.hold_trigger = mg::early_trigger_flag() ? 0 : 1;
-    ml.peer = mgpeer::take_next_peer_sync();  // set by an engine that wants the output all-gathered
+    ml.peer = peer;
     if (ml.peer.world > 1 && ml.n != 1) return (int)cudaErrorInvalidValue;
     const mg::DeviceProps& dp = mg::device_props();
     const int sms = dp.ok ? dp.sm_count : 148;
@@ -407,10 +420,10 @@ int dispatch_multi(const MatList& ml_in, const void* src, int blocks_per_row, cu
 }
 template <int FROM_X>
 int dispatch_dp4a(const uint8_t* w_q4, const void* src, const float* addend, float* y, int out_dim,
-                  int blocks_per_row, cudaStream_t s) {
+                  int blocks_per_row, const mgpeer::PeerSync& peer, cudaStream_t s) {
     MatList ml = {};
     ml.w[0] = w_q4; ml.y[0] = y; ml.addend[0] = addend; ml.rows[0] = out_dim; ml.n = 1;
-    return dispatch_multi<FROM_X>(ml, src, blocks_per_row, s);
+    return dispatch_multi<FROM_X>(ml, src, blocks_per_row, peer, s);
 }
 
 bool fill_matlist(MatList& ml, int n_mats, const uint8_t* const* w, float* const* y, const float* const* addend,
@@ -430,11 +443,13 @@ bool fill_matlist(MatList& ml, int n_mats, const uint8_t* const* w, float* const
 // activation vector convert it once).
 extern "C" int mg_matvec_q4k_limbs_on_stream(const uint8_t* w_q4, const void* records, const float* bias,
                                              float* y, int out_dim, int blocks_per_row, void* stream) {
+    const mgpeer::PeerSync peer = mgpeer::take_next_peer_sync();  // consumed on every path, errors included
     if (out_dim <= 0 || blocks_per_row <= 0) return (int)cudaErrorInvalidValue;
     if (w_q4 == nullptr || records == nullptr || y == nullptr) return (int)cudaErrorInvalidValue;
     if (!mg::aligned16(w_q4) || !mg::aligned16(records)) return (int)cudaErrorInvalidValue;
     if (!limbs_path_ok(blocks_per_row)) return (int)cudaErrorInvalidValue;
-    return dispatch_dp4a<0>(w_q4, records, bias, y, out_dim, blocks_per_row, (cudaStream_t)stream);
+    if (!peer_target_ok(peer, y, (size_t)out_dim * sizeof(float))) return (int)cudaErrorInvalidValue;
+    return dispatch_dp4a<0>(w_q4, records, bias, y, out_dim, blocks_per_row, peer, (cudaStream_t)stream);
 }
 
 // y = dequant(W) . x + bias (bias may be null): the semantics of Op::Matvec
@@ -445,20 +460,35 @@ extern "C" int mg_matvec_q4k_limbs_on_stream(const uint8_t* w_q4, const void* re
 // with a longer x, allocates the scratch and therefore has to precede any stream capture).
 extern "C" int mg_matvec_q4k_bias_on_stream(const uint8_t* w_q4, const float* x, const float* bias,
                                             float* y, int out_dim, int blocks_per_row, void* stream) {
+    const mgpeer::PeerSync peer = mgpeer::take_next_peer_sync();  // consumed on every path, errors included
     if (out_dim <= 0 || blocks_per_row <= 0) return (int)cudaErrorInvalidValue;
     if (w_q4 == nullptr || x == nullptr || y == nullptr) return (int)cudaErrorInvalidValue;
     if (!mg::aligned16(w_q4)) return (int)cudaErrorInvalidValue;
     if (blocks_per_row > 0x7FFFFFFF / 256) return (int)cudaErrorInvalidValue;
+    if (!peer_target_ok(peer, y, (size_t)out_dim * sizeof(float))) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
-    if (!limbs_path_ok(blocks_per_row)) return (int)launch_f32(w_q4, x, bias, y, out_dim, blocks_per_row, s);
-    if (blocks_per_row <= kFusedConvertMaxBpr) return dispatch_dp4a<1>(w_q4, x, bias, y, out_dim, blocks_per_row, s);
+    if (peer.world <= 1 && gemvmma::supported(blocks_per_row)) {
+        // the tensor-core kernel: one launch, x converted inside, no scratch
+        const mg::DeviceProps& dp = mg::device_props();
+        unsigned* timeouts = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&timeouts), g_ring_timeouts);
+        if (e != cudaSuccess) return (int)e;
+        return (int)gemvmma::launch(w_q4, x, bias, y, out_dim, blocks_per_row, mg::early_trigger_flag() ? 0 : 1,
+                                    timeouts, dp.ok ? dp.sm_count : 148, s);
+    }
+    if (!limbs_path_ok(blocks_per_row)) {
+        if (peer.world > 1) return (int)cudaErrorInvalidValue;  // the f32 kernel has no fused exchange
+        return (int)launch_f32(w_q4, x, bias, y, out_dim, blocks_per_row, s);
+    }
+    if (blocks_per_row <= kFusedConvertMaxBpr)
+        return dispatch_dp4a<1>(w_q4, x, bias, y, out_dim, blocks_per_row, peer, s);
     void* ws = nullptr;
     const int k = blocks_per_row * 256;
     cudaError_t e = workspace_for(s, xlimbs::record_bytes((size_t)k), &ws);
     if (e != cudaSuccess) return (int)e;
     const int rc = mg_q4k_x_to_limbs_on_stream(x, k, ws, stream);
     if (rc) return rc;
-    return dispatch_dp4a<0>(w_q4, ws, bias, y, out_dim, blocks_per_row, s);
+    return dispatch_dp4a<0>(w_q4, ws, bias, y, out_dim, blocks_per_row, peer, s);
 }
 
 // Up to three matrices times ONE activation vector in one launch (q/k/v, gate/up):
@@ -468,15 +498,17 @@ extern "C" int mg_matvec_q4k_bias_on_stream(const uint8_t* w_q4, const float* x,
 extern "C" int mg_matvec_q4k_multi_on_stream(int n_mats, const uint8_t* const* w_q4, const void* x,
                                              int x_is_records, const float* const* addend, float* const* y,
                                              const int* out_dims, int blocks_per_row, void* stream) {
+    const mgpeer::PeerSync peer = mgpeer::take_next_peer_sync();  // consumed on every path, errors included
     if (blocks_per_row <= 0 || x == nullptr || !limbs_path_ok(blocks_per_row)) return (int)cudaErrorInvalidValue;
     MatList ml;
     if (!fill_matlist(ml, n_mats, w_q4, y, addend, out_dims)) return (int)cudaErrorInvalidValue;
+    if (!peer_target_ok(peer, ml.y[0], (size_t)ml.rows[0] * sizeof(float))) return (int)cudaErrorInvalidValue;
     if (x_is_records) {
         if (!mg::aligned16(x)) return (int)cudaErrorInvalidValue;
-        return dispatch_multi<0>(ml, x, blocks_per_row, (cudaStream_t)stream);
+        return dispatch_multi<0>(ml, x, blocks_per_row, peer, (cudaStream_t)stream);
     }
     if (blocks_per_row > kFusedConvertMaxBpr) return (int)cudaErrorInvalidValue;
-    return dispatch_multi<1>(ml, x, blocks_per_row, (cudaStream_t)stream);
+    return dispatch_multi<1>(ml, x, blocks_per_row, peer, (cudaStream_t)stream);
 }
 
 // The same with RMSNorm fused in front: y[i] = dequant(w[i]) . (x * rsqrt(mean(x^2)+eps) * norm_weight)
@@ -486,12 +518,14 @@ extern "C" int mg_rmsnorm_matvec_q4k_multi_on_stream(int n_mats, const uint8_t* 
                                                      const float* norm_weight, float eps,
                                                      const float* const* addend, float* const* y,
                                                      const int* out_dims, int blocks_per_row, void* stream) {
+    const mgpeer::PeerSync peer = mgpeer::take_next_peer_sync();  // consumed on every path, errors included
     if (blocks_per_row <= 0 || blocks_per_row > kFusedConvertMaxBpr || !x || !norm_weight) return (int)cudaErrorInvalidValue;
     MatList ml;
     if (!fill_matlist(ml, n_mats, w_q4, y, addend, out_dims)) return (int)cudaErrorInvalidValue;
+    if (!peer_target_ok(peer, ml.y[0], (size_t)ml.rows[0] * sizeof(float))) return (int)cudaErrorInvalidValue;
     ml.norm_w = norm_weight;
     ml.eps = eps;
-    return dispatch_multi<1>(ml, x, blocks_per_row, (cudaStream_t)stream);
+    return dispatch_multi<1>(ml, x, blocks_per_row, peer, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -518,9 +552,11 @@ static __device__ __align__(256) unsigned char g_noalloc_records[kNoAllocMaxBpr 
 // concurrently) race on it: keep calls of this entry point ordered on one stream.
 extern "C" int launch_matvec_q4k_noalloc_on_stream(const uint8_t* w_q4, const float* x, float* y, int out_dim,
                                                    int blocks_per_row, void* stream) {
+    const mgpeer::PeerSync peer = mgpeer::take_next_peer_sync();  // consumed on every path, errors included
     if (out_dim <= 0 || blocks_per_row <= 0) return (int)cudaErrorInvalidValue;
     if (w_q4 == nullptr || x == nullptr || y == nullptr) return (int)cudaErrorInvalidValue;
     if (!mg::aligned16(w_q4)) return (int)cudaErrorInvalidValue;
+    if (!peer_target_ok(peer, y, (size_t)out_dim * sizeof(float))) return (int)cudaErrorInvalidValue;
     if (blocks_per_row > kNoAllocMaxBpr) {
         fprintf(stderr,
                 "launch_matvec_q4k_noalloc_on_stream: blocks_per_row %d exceeds the built-in scratch "
@@ -542,7 +578,7 @@ extern "C" int launch_matvec_q4k_noalloc_on_stream(const uint8_t* w_q4, const fl
     }
     const int rc = mg_q4k_x_to_limbs_on_stream(x, blocks_per_row * 256, dev_ptr[dev], stream);
     if (rc) return rc;
-    return dispatch_dp4a<0>(w_q4, dev_ptr[dev], nullptr, y, out_dim, blocks_per_row, (cudaStream_t)stream);
+    return dispatch_dp4a<0>(w_q4, dev_ptr[dev], nullptr, y, out_dim, blocks_per_row, peer, (cudaStream_t)stream);
 }
 
 extern "C" int launch_matvec_q4k_on_stream(const uint8_t* w_q4, const float* x, float* y, int out_dim,

@@ -42,6 +42,7 @@ cudaError_t launch_gather(const Exchange& ex, int site, size_t offset, size_t my
                           cudaStream_t stream) {
     if (ex.world < 2 || ex.world > kMaxRanks || site < 0 || site >= kMaxSites || !ex.ctl) return cudaErrorInvalidValue;
     if (((offset | my_off | my_bytes) & 3u) != 0 || offset < kFlagBytes) return cudaErrorInvalidValue;
+    if (offset + my_off > ex.bytes || my_bytes > ex.bytes - (offset + my_off)) return cudaErrorInvalidValue;
     Args a;
     a.ps = make_sync(ex, site);
     a.begin = offset + my_off;
@@ -56,6 +57,7 @@ PeerSync make_sync(const Exchange& ex, int site) {
     PeerSync ps;
     for (int r = 0; r < kSyncMaxRanks; ++r) ps.base[r] = r < ex.world ? ex.base[r] : nullptr;
     ps.ctl = ex.ctl;
+    ps.arena_bytes = ex.bytes;
     ps.rank = ex.rank; ps.world = ex.world; ps.site = site;
     return ps;
 }
@@ -96,7 +98,7 @@ int mg_peer_exchange_create(size_t bytes, int rank, int world, void* ipc_handle_
         return (int)cudaErrorInvalidValue;
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
     mg_peer_exchange* x = new mg_peer_exchange();
-    x->ex.rank = rank; x->ex.world = world; x->bytes = bytes;
+    x->ex.rank = rank; x->ex.world = world; x->ex.bytes = bytes; x->bytes = bytes;
     void* arena = nullptr;
     cudaError_t e = cudaMalloc(&arena, bytes);
     if (e == cudaSuccess) e = cudaMemset(arena, 0, bytes);

@@ -29,9 +29,10 @@ struct Exchange {
     int rank = 0, world = 1;
     unsigned char* base[kMaxRanks] = {};  // base[r]: rank r's arena as mapped in this process
     unsigned* ctl = nullptr;              // local control words: epochs, tickets, error (see .cu)
+    size_t bytes = 0;                     // size of the arena (the same on every rank)
 };
 constexpr size_t kCtlWords = 2 * kMaxSites + 1;
-static_assert(kMaxRanks == kSyncMaxRanks && kMaxSites == kSyncMaxSites, "one layout");
+static_assert(kMaxRanks == kSyncMaxRanks && kMaxSites == kSyncMaxSites && kFlagBytes == kSyncFlagBytes, "one layout");
 
 // The device-side view of exchange `site` (what a fused kernel is given).
 PeerSync make_sync(const Exchange& ex, int site);

@@ -15,8 +15,21 @@ constexpr unsigned kSyncSpinLimit = 1u << 22;  // a few seconds of polling (cove
 struct PeerSync {
     unsigned char* base[kSyncMaxRanks];  // base[r]: rank r's arena as mapped in this process
     unsigned* ctl;                       // local: [site] epoch, [kSyncMaxSites + site] ticket, [2*kSyncMaxSites] error
+    unsigned long long arena_bytes;      // size of every rank's arena (all ranks lay theirs out identically)
     int rank, world, site;
 };
+constexpr unsigned long long kSyncFlagBytes = 4096;  // head of every arena: the flags
+
+// Host-side guard for the launchers: [p, p + bytes) lies inside this rank's arena, behind the flags.
+// Peer stores go to the same offset of the peers' arenas, so an output outside the arena would be
+// written at an arbitrary place of another GPU's mapping.
+inline bool in_arena(const PeerSync& ps, const void* p, unsigned long long bytes) {
+    const unsigned char* b = ps.base[ps.rank];
+    const unsigned char* q = static_cast<const unsigned char*>(p);
+    if (b == nullptr || q < b + kSyncFlagBytes) return false;
+    const unsigned long long off = (unsigned long long)(q - b);
+    return off <= ps.arena_bytes && bytes <= ps.arena_bytes - off;
+}
 
 #ifdef __CUDACC__
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {

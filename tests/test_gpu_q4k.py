@@ -105,6 +105,26 @@ def test_matvec_ragged_shapes(orc, out_dim, bpr):
     check_matvec(orc, out_dim, bpr, 7000 + out_dim * 131 + bpr)
 
 
+@pytest.mark.parametrize("name", list(synth.LLAMA_70B_LAYER))
+def test_matvec_llama70b_layer_shapes(orc, name):
+    """The 70B-class projections (rows of 8192 and 28672 weights: 32 and 112 super-blocks)."""
+    out_dim, in_dim = synth.LLAMA_70B_LAYER[name]
+    check_matvec(orc, out_dim, in_dim // 256, 2000 + len(name))
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_matvec_llama70b_per_rank_slices(orc, world):
+    """What one rank of a row-sharded 70B-class layer computes: a contiguous row range of the
+    unmodified block array (k_proj and down_proj: the smallest and the longest-row slices)."""
+    for name in ("k_proj", "down_proj"):
+        out_dim, in_dim = synth.LLAMA_70B_LAYER[name]
+        bpr, rows = in_dim // 256, out_dim // world
+        rng = np.random.Generator(np.random.PCG64(3000 + world))
+        w = synth.q4k_matrix(rows, in_dim, rng)
+        x = synth.activations(in_dim, rng)
+        assert rel_rms_err(gpu_matvec(w, x, rows, bpr), orc.matvec_f64(w, x, rows, bpr)) <= GEMV_TOL
+
+
 def test_matvec_kats(kats):
     for k in kats:
         x = np.array(k["x_ramp"], dtype=np.float32)
@@ -281,3 +301,8 @@ def test_matvec_heavy_tailed_and_nonfinite_activations(orc):
 
 def test_matvec_very_long_rows_take_the_f32_variant(orc):
     check_matvec(orc, 24, 250, 4242)
+
+
+def test_zz_no_gemv_wait_ever_ran_out(cuda):
+    """Every wait inside the GEMV kernels is bounded; none of the launches above may have given up."""
+    assert cuda.mg_matvec_q4k_timeouts() == 0
