@@ -117,6 +117,16 @@ size_t mg_q4k_limb_record_bytes(int k);
  * captured) afterwards; the previous setting is returned. */
 int mg_pdl_early_trigger(int enabled);
 
+/* launch_matvec_q4k / mg_matvec_q4k_bias_on_stream start SPECULATIVELY: the kernel converts x and
+ * computes while the kernel queued before it on the stream may still run, and publishes y only
+ * after that kernel has completed and x has been re-checked against what was converted (results
+ * are exact either way; an x that changed in between costs a second pass).  The launcher already
+ * skips the speculation when x or the bias is the output of the previous matvec it queued on the
+ * same stream.  mg_matvec_q4k_speculation(0) switches it off for the process (also
+ * MODGRAD_Q4K_SPECULATE=0 in the environment), (1) on; the previous setting is returned.  Weights
+ * must not be written by the kernel queued directly before a matvec: they are prefetched early. */
+int mg_matvec_q4k_speculation(int enabled);
+
 /* Health counter of the GEMV kernels on the current device: warps that gave up waiting for a
  * weight copy (every wait in the kernels is bounded).  0 in a healthy process; non-zero means
  * rows of some result were left unwritten.  Synchronises the device; negative = -(CUDA error). */

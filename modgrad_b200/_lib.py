@@ -39,6 +39,7 @@ SIGNATURES = {
     "mg_matvec_q4k_bias_on_stream": (ci, [vp, vp, vp, vp, ci, ci, vp]),
     "mg_q4k_limb_record_bytes": (sz, [ci]),
     "mg_matvec_q4k_timeouts": (C.c_longlong, []),
+    "mg_matvec_q4k_speculation": (ci, [ci]),
     "mg_pdl_early_trigger": (ci, [ci]),
     "mg_peer_exchange_create": (ci, [sz, ci, ci, vp, C.POINTER(vp)]),
     "mg_peer_exchange_open": (ci, [vp, vp]),

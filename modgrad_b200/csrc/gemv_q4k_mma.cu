@@ -23,20 +23,28 @@
 //   limbs of the eight sub-block sums.
 //
 // Pipeline: a CTA owns 16-row tiles (tile = blockIdx.x + i * gridDim.x).  A manager warp streams
-// them into a ring of shared-memory stages with one cp.async.bulk per row (rows padded to a
-// stride of 64 mod 128 bytes: conflict-free 16-byte reads), completion on an mbarrier per
-// stage.  The eight consumer warps split the super-blocks of a stage round-robin, keep per-row
-// partial sums in registers, and after the last window of a tile leave them in shared memory;
-// their arrival on the stage's second mbarrier tells the manager that the stage can be refilled
-// and that the partials can be summed (fixed order: results are deterministic) and stored.
-// Every wait is bounded; a wait that runs out is counted and the CTA drains and returns.
+// them into a ring of shared-memory stages with ONE 2-D tensor-map TMA load per stage (box = 16
+// rows x up to 14 super-blocks; issuing a bulk copy per row instead costs ~40 ns of TMA issue time
+// each and caps the stream), completion on an mbarrier per stage.  Rows lie dense in a stage; the
+// MMA rows are a permutation of the tile rows chosen so that the two rows a quarter-warp reads
+// together are 64 bytes apart modulo 128 (conflict-free 16-byte reads), which needs a window
+// width that is not a multiple of 8 super-blocks.  The eight consumer warps split the
+// super-blocks of a stage round-robin, keep per-row partial sums in registers, and after the last
+// window of a tile leave them in shared memory; their arrival on the stage's second mbarrier
+// tells the manager that the stage can be refilled and that the partials can be summed (fixed
+// order: results are deterministic) and stored.  Every wait is bounded; a wait that runs out is
+// counted and the CTA drains and returns.
 //
 // The first copies are issued BEFORE the kernel waits for its predecessor in the stream
 // (griddepcontrol.wait): weights must not be produced by the kernel launched just before a
 // matvec on the same stream.
 #include "gemv_q4k_mma.hpp"
 
+#include <cuda.h>
+
 #include <float.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 #include "gemv_q4k_device.cuh"
 #include "launch_common.cuh"
@@ -53,7 +61,7 @@ using gemvdev::mbar_try_wait;
 using gemvdev::smem_u32;
 
 constexpr int kConsumerWarps = 8;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kThreads = (kConsumerWarps + 2) * 32;  // consumers, manager, sentinel
 constexpr int kTileRows = 16;
 constexpr int kMaxDepth = 6;
 constexpr int kXBlockBytes = 816;  // per super-block: 768 B limb fragments, 32 B sum fragments, scale, pad
@@ -67,8 +75,13 @@ struct Params {
     int rows, bpr;
     int n_win, kb;      // windows per tile, super-blocks per window (the last may be shorter)
     int depth;          // stages in the ring
-    int row_stride;     // bytes between the rows of a stage
+    int row_stride;     // bytes between the rows of a stage (kb * 144, dense)
+    int row_swap;       // MMA row m reads tile row "m with bits 0 and row_swap exchanged"
     int x_aligned, hold_trigger;
+    int speculate;      // convert x and start computing before the previous kernel has completed
+    // 0xFFFFFFFF, passed at run time so that "w - (w & 0xF0F0F0F0)" stays a multiply-add: the
+    // integer multiply-add runs on the FMA pipe, which has room, the logic pipe does not
+    uint32_t neg_one;
     unsigned* timeouts;
 };
 
@@ -77,21 +90,19 @@ __host__ __device__ inline int round128(int v) { return (v + 127) & ~127; }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One 2-D tiled TMA load (no multicast): box at element coordinates (x, y) of the tensor map.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ void mma_u8s8(int& c0, int& c1, int& c2, int& c3, uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(c0), "+r"(c1), "+r"(c2), "+r"(c3)
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// Bounded wait on an mbarrier phase; false when it ran out or another warp of the CTA gave up.
-__device__ __forceinline__ bool wait_phase(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if (++spins > kSpinLimit || *abort_flag) return false;
-    }
-    return true;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -120,7 +131,10 @@ __device__ __forceinline__ void load8(float (&v)[8], const float* p, int aligned
     }
 }
 
-__device__ __forceinline__ void convert_block(const float (&v)[8], uint8_t* xb, int lane) {
+// VERIFY = false: writes the table of one super-block.  VERIFY = true: writes nothing and returns
+// (to every lane) whether the table differs from what these activations convert to.
+template <bool VERIFY>
+__device__ __forceinline__ bool convert_block(const float (&v)[8], uint8_t* xb, int lane) {
     float amax = 0.f;
     int bad = 0;
 #pragma unroll
@@ -155,6 +169,21 @@ __device__ __forceinline__ void convert_block(const float (&v)[8], uint8_t* xb, 
     }
     const int sub = lane >> 2, G = sub >> 1, h = sub & 1, p = G >> 1;
     const int tlow = (lane & 3) >> 1, j = lane & 1;
+    // A non-finite activation poisons its super-block: every row's sum becomes NaN, as it does in
+    // the reference (w * NaN).
+    const uint32_t s16 = bad ? 0x7FC00000u : (uint32_t)(E - 25 + 127) << 23;  // 2^(E-21) / 16
+    if constexpr (VERIFY) {
+        // The sub-block sums are a function of the limbs: limbs and scale equal => table equal.
+        bool diff = false;
+#pragma unroll
+        for (int n = 0; n < 3; ++n) {
+            const int idx = (G & 1) * 6 + n * 2 + tlow;
+            const uint2 t = *reinterpret_cast<const uint2*>(xb + ((p * 2 + h) * 12 + idx) * 16 + j * 8);
+            diff |= (t.x != lo[n]) | (t.y != hi[n]);
+        }
+        if (lane == 0) diff |= *reinterpret_cast<const uint32_t*>(xb + 800) != s16;
+        return __any_sync(0xFFFFFFFFu, diff);
+    } else {
 #pragma unroll
     for (int n = 0; n < 3; ++n) {
         const int idx = (G & 1) * 6 + n * 2 + tlow;
@@ -175,29 +204,59 @@ __device__ __forceinline__ void convert_block(const float (&v)[8], uint8_t* xb, 
         s[16] = (uint8_t)l2;
         s[24] = (uint8_t)l3;
     }
-    if (lane == 0) {
-        // A non-finite activation poisons its super-block: every row's sum becomes NaN, as it
-        // does in the reference (w * NaN).
-        const float s16 = __uint_as_float((uint32_t)(E - 25 + 127) << 23);  // 2^(E-21) / 16
-        *reinterpret_cast<float*>(xb + 800) = bad ? __uint_as_float(0x7FC00000u) : s16;
+    if (lane == 0) *reinterpret_cast<uint32_t*>(xb + 800) = s16;
+    return false;
     }
+}
+
+// Super-blocks warp, warp + 9, ... of x are converted (or verified) by warp `warp` of the nine
+// working warps; the loads of four super-blocks are in flight at once.  Returns (VERIFY) whether
+// any of the warp's super-blocks no longer matches the table.
+template <bool VERIFY>
+__device__ __noinline__ bool convert_mine(const float* x, int bpr, int x_aligned, uint8_t* xtab, int warp, int lane) {
+    constexpr int kU = 4;
+    constexpr int kWarps = kConsumerWarps + 1;
+    bool diff = false;
+    for (int b0 = warp; b0 < bpr; b0 += kWarps * kU) {
+        float v[kU][8];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int b = b0 + u * kWarps;
+            if (b < bpr) load8(v[u], x + (size_t)b * 256 + lane * 8, x_aligned);
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int b = b0 + u * kWarps;
+            if (b < bpr) diff |= convert_block<VERIFY>(v[u], xtab + (size_t)b * kXBlockBytes, lane);
+        }
+    }
+    return diff;
 }
 
 // Per-lane constants of the MMA fragment layout (g = lane / 4 is the row / column group,
 // t = lane % 4 the slot group).
 struct LaneConst {
     int g, t;
+    int row_a, row_b;     // tile rows behind MMA rows g and g + 8
     int b_active, b_off;  // activation fragment of the limb MMAs: byte offset inside a (p, h) group
     int s_active, s_off;  // activation fragment of the min-term MMA
     uint32_t sel0, sel1;  // byte_perm selectors of the scale for accumulator columns 2t and 2t+1
     float w0, w1;         // limb weights of those columns
     float v0, v1;         // limb weights of the sum columns
+    uint32_t neg_one;
 };
 
-__device__ __forceinline__ LaneConst lane_const(int lane) {
+__device__ __forceinline__ int swap_bits(int m, int k) {  // exchange bits 0 and k of m
+    const int d = ((m >> k) ^ m) & 1;
+    return m ^ (d | (d << k));
+}
+__device__ __forceinline__ LaneConst lane_const(int lane, uint32_t neg_one, int row_swap) {
     LaneConst c;
+    c.neg_one = neg_one;
     c.g = lane >> 2;
     c.t = lane & 3;
+    c.row_a = swap_bits(c.g, row_swap);
+    c.row_b = swap_bits(c.g + 8, row_swap);
     const int n = c.g;
     c.b_active = (n < 3 && c.t < 2) || (n >= 3 && n < 6 && c.t >= 2);
     c.b_off = (n < 3 ? n * 2 + c.t : 6 + (n - 3) * 2 + (c.t - 2)) * 16;
@@ -217,8 +276,8 @@ __device__ __forceinline__ LaneConst lane_const(int lane) {
 // block's operand table.  racc0 / racc1 accumulate rows g and g + 8 (partial over this lane's columns).
 __device__ __forceinline__ void process_block(const uint8_t* blk, int row_stride, const uint8_t* xb,
                                               const LaneConst& lc, float& racc0, float& racc1) {
-    const uint8_t* r0p = blk + lc.g * row_stride;
-    const uint8_t* r1p = r0p + 8 * row_stride;
+    const uint8_t* r0p = blk + lc.row_a * row_stride;
+    const uint8_t* r1p = blk + lc.row_b * row_stride;
     const uint4 h0 = *reinterpret_cast<const uint4*>(r0p);
     const uint4 h1 = *reinterpret_cast<const uint4*>(r1p);
     const float2 dd0 = __half22float2(*reinterpret_cast<const __half2*>(&h0.x));
@@ -247,14 +306,25 @@ __device__ __forceinline__ void process_block(const uint8_t* blk, int row_stride
         const uint4 q1 = *reinterpret_cast<const uint4*>(r1p + 16 + p * 64 + lc.t * 16);
         const uint32_t scw0 = p ? s0.sc_hi : s0.sc_lo;
         const uint32_t scw1 = p ? s1.sc_hi : s1.sc_lo;
+        // high nibbles in place (16 * q) with one logic op, low nibbles as w - 16 * q on the FMA pipe
+        const uint32_t w0[4] = {q0.x, q0.y, q0.z, q0.w}, w1[4] = {q1.x, q1.y, q1.z, q1.w};
+        uint32_t hq0[4], hq1[4], lq0[4], lq1[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            hq0[k] = w0[k] & 0xF0F0F0F0u;
+            hq1[k] = w1[k] & 0xF0F0F0F0u;
+            lq0[k] = hq0[k] * lc.neg_one + w0[k];
+            lq1[k] = hq1[k] * lc.neg_one + w1[k];
+        }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             uint4 bf = make_uint4(0u, 0u, 0u, 0u);
             if (lc.b_active) bf = *reinterpret_cast<const uint4*>(xb + (p * 2 + h) * 192 + lc.b_off);
-            const uint32_t mask = h ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
             int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
-            mma_u8s8(c0, c1, c2, c3, q0.x & mask, q1.x & mask, q0.y & mask, q1.y & mask, bf.x, bf.y);
-            mma_u8s8(c0, c1, c2, c3, q0.z & mask, q1.z & mask, q0.w & mask, q1.w & mask, bf.z, bf.w);
+            mma_u8s8(c0, c1, c2, c3, h ? hq0[0] : lq0[0], h ? hq1[0] : lq1[0], h ? hq0[1] : lq0[1],
+                     h ? hq1[1] : lq1[1], bf.x, bf.y);
+            mma_u8s8(c0, c1, c2, c3, h ? hq0[2] : lq0[2], h ? hq1[2] : lq1[2], h ? hq0[3] : lq0[3],
+                     h ? hq1[3] : lq1[3], bf.z, bf.w);
             const int sc00 = (int)__byte_perm(scw0, 0u, lc.sel0 + h), sc01 = (int)__byte_perm(scw0, 0u, lc.sel1 + h);
             const int sc10 = (int)__byte_perm(scw1, 0u, lc.sel0 + h), sc11 = (int)__byte_perm(scw1, 0u, lc.sel1 + h);
             if (h == 0) {
@@ -277,159 +347,295 @@ __device__ __forceinline__ void process_block(const uint8_t* blk, int row_stride
     racc1 = fmaf(-(m1 * s_b) * 16.0f, n1, racc1);
 }
 
-__global__ void __launch_bounds__(kThreads, 2) matvec_q4k_mma_kernel(const Params p) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full_bar[kMaxDepth];
-    __shared__ __align__(8) uint64_t done_bar[kMaxDepth];
-    __shared__ int abort_word;
-    volatile int* abort_flag = &abort_word;
+// Control words of a CTA (shared memory).
+struct Control {
+    uint64_t full_bar[kMaxDepth];  // stage filled (transaction bytes)
+    uint64_t done_bar[kMaxDepth];  // stage consumed (eight consumer warps)
+    uint64_t verified_bar;         // the nine working warps have re-checked their part of x
+    int abort;                     // a bounded wait ran out somewhere in the CTA
+    int released;                  // the previous kernel of the stream has completed (set by the sentinel warp)
+    int mismatch;                  // x changed after it was converted speculatively
+    int verdict;                   // 0 unknown, 1 the speculative operand table is valid, 2 it is not
+};
+constexpr int kVerdictOk = 1, kVerdictRedo = 2;
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+__device__ __forceinline__ int ld_volatile(const int* p) { return *reinterpret_cast<const volatile int*>(p); }
+
+// One pass over this CTA's tiles.
+//   SPEC = true : x was converted BEFORE the previous kernel of the stream is known to have completed.
+//                 Results are kept in shared memory until the sentinel warp reports the table valid
+//                 (verdict 1: flush and continue storing directly) or stale (verdict 2: give up, the
+//                 caller runs the pass again with SPEC = false).  Every working warp re-checks its
+//                 share of x as soon as `released` is set, whatever it is doing.
+//   SPEC = false: x is final; results are stored directly.
+// Returns false when a bounded wait ran out.
+template <bool SPEC>
+__device__ __forceinline__ void run_pass(const Params& p, const CUtensorMap* wmap, Control* c, uint8_t* xtab,
+                                         float* partials, float* results, uint8_t* stages, int warp, int lane) {
     const int depth = p.depth;
     const int stage_bytes = kTileRows * p.row_stride;
-    uint8_t* xtab = smem;
-    float* partials = reinterpret_cast<float*>(smem + round128(p.bpr * kXBlockBytes));  // [depth+1][8][16]
-    uint8_t* stages = reinterpret_cast<uint8_t*>(partials) + round128((depth + 1) * kConsumerWarps * kTileRows * 4);
-    const size_t row_bytes = (size_t)p.bpr * q4k::kBlockBytes;
     const int n_tiles = (p.rows + kTileRows - 1) / kTileRows;
     const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const int total = my_tiles * p.n_win;  // stage uses of this CTA
+    volatile int* abort_flag = &c->abort;
+    bool verified = !SPEC;  // this warp has re-checked its share of x
 
-    if (!p.hold_trigger) griddep_launch_dependents();
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < depth; ++s) {
-            mbar_init(full_bar + s, 1);
-            mbar_init(done_bar + s, kConsumerWarps);
+    // Re-check of this warp's share of x once the previous kernel has completed; called from every
+    // loop and every wait so that the verdict never waits for a warp that is busy or blocked.
+    auto poll_verify = [&]() {
+        if (verified || !ld_volatile(&c->released)) return;
+        const bool diff = convert_mine<true>(p.x, p.bpr, p.x_aligned, xtab, warp, lane);
+        if (lane == 0) {
+            if (diff) atomicOr(&c->mismatch, 1);
+            mbar_arrive(&c->verified_bar);
         }
-        abort_word = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-
-    // Fills the stage of use `u` (tile u / n_win, window u % n_win); all lanes of the manager warp call it.
-    auto issue = [&](int u) {
-        const int ti = u / p.n_win, win = u - ti * p.n_win;
-        const int row0 = ((int)blockIdx.x + ti * (int)gridDim.x) * kTileRows;
-        const int valid = min(kTileRows, p.rows - row0);
-        const int b0 = win * p.kb;
-        const uint32_t bytes = (uint32_t)(min(p.kb, p.bpr - b0) * q4k::kBlockBytes);
-        const int s = u % depth;
-        if (lane == 0) mbar_arrive_expect_tx(full_bar + s, bytes * (uint32_t)valid);
-        __syncwarp();
-        if (lane < valid)
-            bulk_copy_g2s(stages + (size_t)s * stage_bytes + lane * p.row_stride,
-                          p.w + (size_t)(row0 + lane) * row_bytes + (size_t)b0 * q4k::kBlockBytes, bytes, full_bar + s);
+        verified = true;
+    };
+    // Bounded wait for an mbarrier phase that keeps the verification going; false: give up / abort.
+    auto wait_bar = [&](uint64_t* bar, uint32_t parity) {
+        uint32_t spins = 0;
+        while (!mbar_try_wait(bar, parity)) {
+            if (SPEC) {
+                poll_verify();
+                if (ld_volatile(&c->verdict) == kVerdictRedo) return false;
+            }
+            if (++spins > kSpinLimit || *abort_flag) {
+                if (lane == 0 && !*abort_flag) {
+                    atomicAdd(p.timeouts, 1u);
+                    *abort_flag = 1;
+                }
+                return false;
+            }
+        }
+        return true;
     };
 
-    int issued = 0;
-    if (warp == kConsumerWarps) {  // weights do not depend on the previous kernel
-        for (; issued < depth && issued < total; ++issued) issue(issued);
-    }
+    // Fills the stage of use `u` (tile u / n_win, window u % n_win) with one TMA load: the box is
+    // always whole (rows past the matrix and super-blocks past the row arrive as zeros).
+    auto issue = [&](int u) {
+        if (lane != 0) return;
+        const int ti = u / p.n_win, win = u - ti * p.n_win;
+        const int row0 = ((int)blockIdx.x + ti * (int)gridDim.x) * kTileRows;
+        const int s = u % depth;
+        mbar_arrive_expect_tx(c->full_bar + s, (uint32_t)stage_bytes);
+        tma_load_2d(stages + (size_t)s * stage_bytes, wmap, win * p.kb * (q4k::kBlockBytes / 8), row0, c->full_bar + s);
+    };
 
-    griddep_wait();  // x may be produced by the kernel launched just before this one
-
-    {   // every warp converts super-blocks warp, warp + 9, ...; loads of four blocks in flight at once
-        constexpr int kU = 4;
-        constexpr int kWarps = kConsumerWarps + 1;
-        for (int b0 = warp; b0 < p.bpr; b0 += kWarps * kU) {
-            float v[kU][8];
-#pragma unroll
-            for (int u = 0; u < kU; ++u) {
-                const int b = b0 + u * kWarps;
-                if (b < p.bpr) load8(v[u], p.x + (size_t)b * 256 + lane * 8, p.x_aligned);
-            }
-#pragma unroll
-            for (int u = 0; u < kU; ++u) {
-                const int b = b0 + u * kWarps;
-                if (b < p.bpr) convert_block(v[u], xtab + (size_t)b * kXBlockBytes, lane);
-            }
-        }
-    }
-    __syncthreads();
-
+    // Which warp takes super-block b of a tile: (b + phase) % 8, phase = (tile counter * bpr) % 8,
+    // so that over consecutive tiles every warp gets the same number of super-blocks.  A warp's
+    // partial sum of a tile therefore holds the blocks b = j (mod 8) for j = (warp - phase) % 8, and
+    // the manager adds the partials in the order j = 0..7: the summation order of a row does not
+    // depend on where the row sits in the matrix.
     if (warp == kConsumerWarps) {
-        // ---- manager: refill stages as they are released, finish tiles -------------------------
-        int ti = 0, win = 0, u = 0;
-        bool ok = true;
+        // ---- manager: fill stages, refill them as they are released, finish tiles -----------------
+        int issued = 0;
+        for (; issued < depth && issued < total; ++issued) issue(issued);
+        int ti = 0, win = 0, u = 0, s = 0, pidx = 0, phase = 0, flushed = 0;
+        uint32_t par = 0;
+        bool direct = !SPEC;  // results go straight to y
+        // y[row] of local tile `t` from its sum
+        auto store_row = [&](int t, float sum) {
+            const int row = ((int)blockIdx.x + t * (int)gridDim.x) * kTileRows + lane;
+            if (lane < kTileRows && row < p.rows) p.y[row] = p.addend != nullptr ? sum + p.addend[row] : sum;
+        };
+        auto maybe_flush = [&]() {  // the table turned out valid: write what was held back
+            if (direct || ld_volatile(&c->verdict) != kVerdictOk) return;
+            for (; flushed < ti; ++flushed) store_row(flushed, lane < kTileRows ? results[flushed * kTileRows + lane] : 0.0f);
+            direct = true;
+        };
+        bool alive = true;
         for (; u < total; ++u) {
-            const int s = u % depth;
-            if (!wait_phase(done_bar + s, (uint32_t)(u / depth) & 1u, abort_flag)) {
-                ok = false;
+            if (!wait_bar(c->done_bar + s, par)) {
+                alive = false;
                 break;
             }
             if (issued < total) issue(issued++);
             if (win == p.n_win - 1) {
+                float sum = 0.0f;
                 if (lane < kTileRows) {
-                    const int row = ((int)blockIdx.x + ti * (int)gridDim.x) * kTileRows + lane;
-                    if (row < p.rows) {
-                        const float* pp = partials + (size_t)(ti % (depth + 1)) * kConsumerWarps * kTileRows + lane;
-                        float sum = 0.0f;
+                    const float* pp = partials + (size_t)pidx * kConsumerWarps * kTileRows + lane;
 #pragma unroll
-                        for (int w = 0; w < kConsumerWarps; ++w) sum += pp[w * kTileRows];
-                        if (p.addend != nullptr) sum += p.addend[row];
-                        p.y[row] = sum;
-                    }
+                    for (int j = 0; j < kConsumerWarps; ++j) sum += pp[((phase + j) & 7) * kTileRows];
                 }
+                if (SPEC) maybe_flush();
+                if (direct) store_row(ti, sum);
+                else if (lane < kTileRows) results[ti * kTileRows + lane] = sum;
                 win = 0;
                 ++ti;
+                phase = (phase + p.bpr) & 7;
+                if (++pidx > depth) pidx = 0;
             } else {
                 ++win;
             }
-        }
-        if (!ok) {
-            // Never expected.  Report, stop the consumers, and let the copies still in flight land
-            // before the CTA (and its shared memory) goes away.
-            if (lane == 0) {
-                atomicAdd(p.timeouts, 1u);
-                *abort_flag = 1;
+            if (++s == depth) {
+                s = 0;
+                par ^= 1u;
             }
-            __syncwarp();
-            for (int v = u; v < issued; ++v) {
-                uint32_t spins = 0;
-                while (!mbar_try_wait(full_bar + v % depth, (uint32_t)(v / depth) & 1u) && ++spins < kSpinLimit) {
+        }
+        if (SPEC && alive) {  // everything computed: wait for the verdict, then publish
+            uint32_t spins = 0;
+            while (!ld_volatile(&c->verdict)) {
+                poll_verify();
+                __nanosleep(100);
+                if (++spins > kSpinLimit || *abort_flag) {
+                    if (lane == 0 && !*abort_flag) {
+                        atomicAdd(p.timeouts, 1u);
+                        *abort_flag = 1;
+                    }
+                    break;
                 }
+            }
+            maybe_flush();
+        }
+        if (!alive) {
+            // Gave up (stale table, or a wait that ran out): let the copies still in flight land before
+            // the stages are reused or the CTA goes away.
+            for (int v = max(0, issued - depth); v < issued; ++v) {
+                uint32_t spins = 0;
+                while (!mbar_try_wait(c->full_bar + v % depth, (uint32_t)(v / depth) & 1u) && ++spins < kSpinLimit) {
+                }
+            }
+        }
+        if (SPEC) {  // the verification needs every working warp, also after a stale verdict or an abort
+            uint32_t spins = 0;
+            while (!verified && ++spins < kSpinLimit && !*abort_flag) {
+                poll_verify();
+                if (!verified) __nanosleep(100);
             }
         }
     } else {
         // ---- consumers ---------------------------------------------------------------------------
-        const LaneConst lc = lane_const(lane);
+        const LaneConst lc = lane_const(lane, p.neg_one, p.row_swap);
         float racc0 = 0.0f, racc1 = 0.0f;
-        int ti = 0, win = 0, blk_seq = 0;
+        int win = 0, s = 0, pidx = 0, phase = 0;
+        uint32_t par = 0;
         for (int u = 0; u < total; ++u) {
-            const int s = u % depth;
-            if (!wait_phase(full_bar + s, (uint32_t)(u / depth) & 1u, abort_flag)) {
-                if (lane == 0) {
-                    atomicAdd(p.timeouts, 1u);
-                    *abort_flag = 1;
-                }
-                break;
+            if (SPEC) {
+                poll_verify();
+                if (ld_volatile(&c->verdict) == kVerdictRedo) break;
             }
+            if (!wait_bar(c->full_bar + s, par)) break;
             const int b0 = win * p.kb;
             const int nb = min(p.kb, p.bpr - b0);
             const uint8_t* stage = stages + (size_t)s * stage_bytes;
-            for (int i = (warp - blk_seq) & 7; i < nb; i += kConsumerWarps)
+            for (int i = (warp - phase - b0) & 7; i < nb; i += kConsumerWarps)
                 process_block(stage + i * q4k::kBlockBytes, p.row_stride, xtab + (size_t)(b0 + i) * kXBlockBytes, lc,
                               racc0, racc1);
-            blk_seq = (blk_seq + nb) & 7;
             if (win == p.n_win - 1) {
                 racc0 += __shfl_xor_sync(0xFFFFFFFFu, racc0, 1);
                 racc0 += __shfl_xor_sync(0xFFFFFFFFu, racc0, 2);
                 racc1 += __shfl_xor_sync(0xFFFFFFFFu, racc1, 1);
                 racc1 += __shfl_xor_sync(0xFFFFFFFFu, racc1, 2);
                 if (lc.t == 0) {
-                    float* pp = partials + ((size_t)(ti % (depth + 1)) * kConsumerWarps + warp) * kTileRows;
-                    pp[lc.g] = racc0;
-                    pp[lc.g + 8] = racc1;
+                    float* pp = partials + ((size_t)pidx * kConsumerWarps + warp) * kTileRows;
+                    pp[lc.row_a] = racc0;
+                    pp[lc.row_b] = racc1;
                 }
                 racc0 = racc1 = 0.0f;
                 win = 0;
-                ++ti;
+                phase = (phase + p.bpr) & 7;
+                if (++pidx > depth) pidx = 0;
             } else {
                 ++win;
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(done_bar + s);
+            if (lane == 0) mbar_arrive(c->done_bar + s);
+            if (++s == depth) {
+                s = 0;
+                par ^= 1u;
+            }
         }
+        if (SPEC) {
+            uint32_t spins = 0;
+            while (!verified && ++spins < kSpinLimit && !*abort_flag) {
+                poll_verify();
+                if (!verified) __nanosleep(100);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void init_barriers(Control* c, int depth) {
+    for (int s = 0; s < depth; ++s) {
+        mbar_init(c->full_bar + s, 1);
+        mbar_init(c->done_bar + s, kConsumerWarps);
+    }
+    mbar_init(&c->verified_bar, kConsumerWarps + 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// Warps 0..7 consume, warp 8 manages the ring and the results, warp 9 (the sentinel) does nothing
+// but wait for the previous kernel of the stream and judge the speculation.
+__global__ void __launch_bounds__(kThreads, 2)
+matvec_q4k_mma_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) Control ctl;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tiles = (p.rows + kTileRows - 1) / kTileRows;
+    const int max_tiles = (n_tiles + (int)gridDim.x - 1) / (int)gridDim.x;
+    uint8_t* xtab = smem;
+    float* partials = reinterpret_cast<float*>(smem + round128(p.bpr * kXBlockBytes));  // [depth+1][8][16]
+    float* results = partials + (p.depth + 1) * kConsumerWarps * kTileRows;              // [max_tiles][16]
+    uint8_t* stages = smem + round128(p.bpr * kXBlockBytes) +
+                      round128(((p.depth + 1) * kConsumerWarps + max_tiles) * kTileRows * 4);
+    const bool working = warp <= kConsumerWarps;
+
+    if (!p.hold_trigger) griddep_launch_dependents();
+    if (threadIdx.x == 0) {
+        init_barriers(&ctl, p.depth);
+        ctl.abort = 0;
+        ctl.released = 0;
+        ctl.mismatch = 0;
+        ctl.verdict = 0;
+    }
+    __syncthreads();
+
+    if (p.speculate) {
+        if (working) {
+            // x as it is NOW: the kernel before this one may still be running (and writing it)
+            convert_mine<false>(p.x, p.bpr, p.x_aligned, xtab, warp, lane);
+            asm volatile("bar.sync 1, %0;" ::"n"((kConsumerWarps + 1) * 32) : "memory");
+            run_pass<true>(p, &wmap, &ctl, xtab, partials, results, stages, warp, lane);
+        } else {
+            griddep_wait();  // the kernel launched just before this one has completed
+            if (lane == 0) {
+                __threadfence_block();
+                *reinterpret_cast<volatile int*>(&ctl.released) = 1;
+                uint32_t spins = 0;
+                bool ok = true;
+                while (!mbar_try_wait(&ctl.verified_bar, 0u)) {
+                    if (++spins > kSpinLimit || ld_volatile(&ctl.abort)) {
+                        ok = false;
+                        break;
+                    }
+                }
+                if (!ok && !ld_volatile(&ctl.abort)) {
+                    atomicAdd(p.timeouts, 1u);
+                    *reinterpret_cast<volatile int*>(&ctl.abort) = 1;
+                }
+                __threadfence_block();
+                *reinterpret_cast<volatile int*>(&ctl.verdict) = (ok && !ld_volatile(&ctl.mismatch)) ? kVerdictOk : kVerdictRedo;
+            }
+        }
+        __syncthreads();
+        if (ctl.verdict == kVerdictOk || ctl.abort) return;
+        // x changed under the speculation: start over on the final x
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < p.depth; ++s) {
+                asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(ctl.full_bar + s)) : "memory");
+                asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(ctl.done_bar + s)) : "memory");
+            }
+            asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&ctl.verified_bar)) : "memory");
+            init_barriers(&ctl, p.depth);
+        }
+        __syncthreads();
+    } else {
+        griddep_wait();  // x may be produced by the kernel launched just before this one
+    }
+    if (working) {
+        convert_mine<false>(p.x, p.bpr, p.x_aligned, xtab, warp, lane);
+        asm volatile("bar.sync 1, %0;" ::"n"((kConsumerWarps + 1) * 32) : "memory");
+        run_pass<false>(p, &wmap, &ctl, xtab, partials, results, stages, warp, lane);
     }
 }
 
@@ -440,33 +646,42 @@ namespace {
 
 constexpr int kSmemTwoPerSm = 115456;  // two CTAs per SM: 2 x (this + static + 1 KiB reserved) <= 228 KiB
 constexpr int kSmemOnePerSm = 226 * 1024;
-
-int pad_row_stride(int bytes) {  // next multiple of 16 that is 64 mod 128
-    int s = (bytes + 15) & ~15;
-    while ((s & 127) != 64) s += 16;
-    return s;
-}
+constexpr int kMaxWindow = 14;  // super-blocks per stage row: 14 * 18 eight-byte elements <= 256 (TMA box limit)
 
 struct Config {
-    int n_win = 0, kb = 0, depth = 0, row_stride = 0, smem = 0;
+    int n_win = 0, kb = 0, depth = 0, row_swap = 0, smem = 0;
 };
 
+// Rows lie dense in a stage (kb * 144 bytes apart).  The two tile rows a quarter-warp reads together
+// must be 64 bytes apart modulo 128: rows r and r + 2^k with 2^k * kb = 4 (mod 8); none exists when
+// kb is a multiple of 8.
+int row_swap_for(int kb) {
+    for (int k = 0; k < 3; ++k)
+        if ((((1 << k) * kb) & 7) == 4) return k;
+    return -1;
+}
+
 // The ring that keeps the most weight bytes in flight inside `budget` bytes of shared memory.
-bool pick_config(int bpr, int budget, Config& best) {
+bool pick_config(int bpr, int budget, int max_tiles, Config& best) {
     const int xtab = round128(bpr * kXBlockBytes);
     long best_flight = -1;
-    for (int n_win = 1; n_win <= bpr; ++n_win) {
-        const int kb = (bpr + n_win - 1) / n_win;
-        if ((bpr + kb - 1) / kb != n_win) continue;  // same windows as a smaller n_win
-        const int row_stride = pad_row_stride(kb * q4k::kBlockBytes);
-        const int stage = kTileRows * row_stride;
+    for (int n_win = (bpr + kMaxWindow - 1) / kMaxWindow; n_win <= bpr; ++n_win) {
+        int kb = (bpr + n_win - 1) / n_win;
+        if ((kb & 7) == 0) {  // widen the window by one if the split stays valid
+            if (kb + 1 > kMaxWindow || (n_win - 1) * (kb + 1) >= bpr) continue;
+            ++kb;
+        }
+        if ((n_win - 1) * kb >= bpr) continue;
+        const int swap = row_swap_for(kb);
+        if (swap < 0) continue;
+        const int stage = kTileRows * kb * q4k::kBlockBytes;
         for (int depth = kMaxDepth; depth >= 3; --depth) {
-            const int smem = xtab + round128((depth + 1) * kConsumerWarps * kTileRows * 4) + depth * stage;
+            const int smem = xtab + round128(((depth + 1) * kConsumerWarps + max_tiles) * kTileRows * 4) + depth * stage;
             if (smem > budget) continue;
-            const long flight = (long)(depth - 1) * kTileRows * kb * q4k::kBlockBytes;
+            const long flight = (long)(depth - 1) * stage;
             if (flight > best_flight) {
                 best_flight = flight;
-                best = Config{n_win, kb, depth, row_stride, smem};
+                best = Config{n_win, kb, depth, swap, smem};
             }
             break;
         }
@@ -474,21 +689,62 @@ bool pick_config(int bpr, int budget, Config& best) {
     return best_flight >= 0;
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// cuTensorMapEncodeTiled through the runtime (the library does not link libcuda).
+EncodeTiledFn encode_tiled() {
+    static const EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
 }  // namespace
 
 bool supported(int blocks_per_row) {
     Config c;
-    return blocks_per_row > 0 && pick_config(blocks_per_row, kSmemOnePerSm, c);
+    return blocks_per_row > 0 && encode_tiled() != nullptr && pick_config(blocks_per_row, kSmemOnePerSm, 64, c);
 }
 
 cudaError_t launch(const uint8_t* w, const float* x, const float* addend, float* y, int rows, int bpr,
-                   int hold_trigger, unsigned* timeouts, int sms, cudaStream_t stream) {
+                   int hold_trigger, int speculate, unsigned* timeouts, int sms, cudaStream_t stream) {
     Config c;
+    const int n_tiles = (rows + kTileRows - 1) / kTileRows;
+    const int grid = n_tiles < sms ? n_tiles : sms;
+    const int max_tiles = (n_tiles + grid - 1) / grid;
     // Half an SM when a useful ring fits beside the operand table (the successor kernel can then be
     // resident early); the whole SM for long rows.
-    const bool two = pick_config(bpr, kSmemTwoPerSm, c) &&
-                     (long)(c.depth - 1) * kTileRows * c.kb * q4k::kBlockBytes >= 48 * 1024;
-    if (!two && !pick_config(bpr, kSmemOnePerSm, c)) return cudaErrorInvalidValue;
+    const bool two = pick_config(bpr, kSmemTwoPerSm, max_tiles, c) && (long)(c.depth - 1) * kTileRows * c.kb * q4k::kBlockBytes >= 48 * 1024;
+    if (!two && !pick_config(bpr, kSmemOnePerSm, max_tiles, c)) return cudaErrorInvalidValue;
+    {   // BRING-UP override: MODGRAD_MMA_CFG="n_win,depth,budget_kb"
+        const char* e = getenv("MODGRAD_MMA_CFG");
+        int nw = 0, dp = 0, kb_ = 0;
+        if (e && sscanf(e, "%d,%d,%d", &nw, &dp, &kb_) == 3 && nw >= 1 && nw <= bpr && dp >= 2 && dp <= kMaxDepth) {
+            Config o;
+            o.n_win = nw; o.kb = (bpr + nw - 1) / nw; o.depth = dp;
+            o.row_swap = row_swap_for(o.kb);
+            o.smem = round128(bpr * kXBlockBytes) + round128(((dp + 1) * kConsumerWarps + max_tiles) * kTileRows * 4) + dp * kTileRows * o.kb * q4k::kBlockBytes;
+            if (o.smem <= kb_ * 1024 && o.row_swap >= 0 && o.kb <= kMaxWindow && (nw - 1) * o.kb < bpr) c = o;
+        }
+    }
+    const EncodeTiledFn encode = encode_tiled();
+    if (encode == nullptr) return cudaErrorNotSupported;
+    // The weight matrix as a 2-D tensor of 8-byte elements: [rows][bpr * 18]; box = 16 rows x kb * 18.
+    CUtensorMap wmap;
+    const cuuint64_t gdim[2] = {(cuuint64_t)bpr * 18u, (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)bpr * q4k::kBlockBytes};
+    const cuuint32_t box[2] = {(cuuint32_t)c.kb * 18u, (cuuint32_t)kTileRows};
+    const cuuint32_t estride[2] = {1u, 1u};
+    if (encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(w), gdim, gstride, box, estride,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -504,13 +760,13 @@ cudaError_t launch(const uint8_t* w, const float* x, const float* addend, float*
     Params p = {};
     p.w = w; p.x = x; p.addend = addend; p.y = y;
     p.rows = rows; p.bpr = bpr;
-    p.n_win = c.n_win; p.kb = c.kb; p.depth = c.depth; p.row_stride = c.row_stride;
+    p.n_win = c.n_win; p.kb = c.kb; p.depth = c.depth; p.row_stride = c.kb * q4k::kBlockBytes; p.row_swap = c.row_swap;
     p.x_aligned = mg::aligned16(x) ? 1 : 0;
     p.hold_trigger = hold_trigger;
+    p.speculate = speculate;
     p.timeouts = timeouts;
-    const int n_tiles = (rows + kTileRows - 1) / kTileRows;
-    const int grid = n_tiles < sms ? n_tiles : sms;
-    return mg::launch_pdl(matvec_q4k_mma_kernel, dim3((unsigned)grid), dim3(kThreads), (size_t)c.smem, stream, p);
+    p.neg_one = 0xFFFFFFFFu;
+    return mg::launch_pdl(matvec_q4k_mma_kernel, dim3((unsigned)grid), dim3(kThreads), (size_t)c.smem, stream, p, wmap);
 }
 
 }  // namespace gemvmma

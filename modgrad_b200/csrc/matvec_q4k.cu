@@ -32,6 +32,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include <atomic>
 #include <map>
 #include <mutex>
 
@@ -333,6 +334,41 @@ cudaError_t workspace_for(cudaStream_t stream, size_t bytes, void** out) {
 // conversion kernel plus a scratch table.
 constexpr int kFusedConvertMaxBpr = 32;
 
+// Speculation of the tensor-core GEMV (gemv_q4k_mma.cu): it converts x and computes while the kernel
+// queued before it may still run, and publishes only after x has been re-checked.  A stale x costs
+// a second pass, so the launcher does not speculate when it KNOWS the input is still being produced:
+// when x or the addend overlaps the output of the previous matvec this library queued on the same
+// stream.  (Kernels of other libraries in between are invisible here; the re-check covers them.)
+std::atomic<int> g_speculation{-1};  // -1: not read from the environment yet
+struct LastOutput {
+    const char* lo = nullptr;
+    const char* hi = nullptr;
+};
+std::mutex g_last_mu;
+std::map<std::pair<int, cudaStream_t>, LastOutput> g_last_out;
+
+bool overlaps(const void* p, size_t n, const LastOutput& o) {
+    const char* a = static_cast<const char*>(p);
+    return p != nullptr && o.lo != nullptr && a < o.hi && o.lo < a + n;
+}
+int speculation_for(cudaStream_t stream, const void* x, size_t x_bytes, const void* addend, const void* y,
+                    size_t y_bytes) {
+    int on = g_speculation.load(std::memory_order_relaxed);
+    if (on < 0) {
+        const char* e = getenv("MODGRAD_Q4K_SPECULATE");
+        on = (e && e[0] == '0') ? 0 : 1;
+        g_speculation.store(on, std::memory_order_relaxed);
+    }
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(g_last_mu);
+    LastOutput& last = g_last_out[{dev, stream}];
+    const bool dependent = overlaps(x, x_bytes, last) || overlaps(addend, y_bytes, last);
+    last.lo = static_cast<const char*>(y);
+    last.hi = last.lo + y_bytes;
+    return on && !dependent ? 1 : 0;
+}
+
 // An armed exchange stores the output at the same offset of every peer's arena: the target must
 // lie inside this rank's arena, behind the flag block.
 bool peer_target_ok(const mgpeer::PeerSync& ps, const void* out, size_t bytes) {
@@ -394,6 +430,13 @@ extern "C" long long mg_matvec_q4k_timeouts(void) {
     unsigned n = 0;
     const cudaError_t e = cudaMemcpyFromSymbol(&n, g_ring_timeouts, sizeof(n));
     return e == cudaSuccess ? (long long)n : -(long long)e;
+}
+
+// Switches the speculative start of launch_matvec_q4k / mg_matvec_q4k_bias_on_stream on (default) or
+// off for the whole process; returns the previous setting.
+extern "C" int mg_matvec_q4k_speculation(int enabled) {
+    int prev = g_speculation.exchange(enabled ? 1 : 0);
+    return prev < 0 ? 1 : prev;
 }
 
 extern "C" size_t mg_q4k_limb_record_bytes(int k) { return k > 0 ? xlimbs::record_bytes((size_t)k) : 0; }
@@ -474,6 +517,8 @@ extern "C" int mg_matvec_q4k_bias_on_stream(const uint8_t* w_q4, const float* x,
         cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&timeouts), g_ring_timeouts);
         if (e != cudaSuccess) return (int)e;
         return (int)gemvmma::launch(w_q4, x, bias, y, out_dim, blocks_per_row, mg::early_trigger_flag() ? 0 : 1,
+                                    speculation_for(s, x, (size_t)blocks_per_row * 256 * sizeof(float), bias, y,
+                                                    (size_t)out_dim * sizeof(float)),
                                     timeouts, dp.ok ? dp.sm_count : 148, s);
     }
     if (!limbs_path_ok(blocks_per_row)) {
