@@ -43,8 +43,6 @@
 #include <cuda.h>
 
 #include <float.h>
-#include <stdio.h>
-#include <stdlib.h>
 
 #include "gemv_q4k_device.cuh"
 #include "launch_common.cuh"
@@ -131,10 +129,10 @@ __device__ __forceinline__ void load8(float (&v)[8], const float* p, int aligned
     }
 }
 
-// VERIFY = false: writes the table of one super-block.  VERIFY = true: writes nothing and returns
-// (to every lane) whether the table differs from what these activations convert to.
-template <bool VERIFY>
-__device__ __forceinline__ bool convert_block(const float (&v)[8], uint8_t* xb, int lane) {
+// verify = false: writes the table of one super-block.  verify = true: writes nothing and returns
+// (to every lane) whether the table differs from what these activations convert to.  (One body
+// for both, and rolled loops around it: the kernel's instruction footprint matters.)
+__device__ __forceinline__ bool convert_block(const float (&v)[8], uint8_t* xb, int lane, bool verify) {
     float amax = 0.f;
     int bad = 0;
 #pragma unroll
@@ -172,7 +170,7 @@ __device__ __forceinline__ bool convert_block(const float (&v)[8], uint8_t* xb, 
     // A non-finite activation poisons its super-block: every row's sum becomes NaN, as it does in
     // the reference (w * NaN).
     const uint32_t s16 = bad ? 0x7FC00000u : (uint32_t)(E - 25 + 127) << 23;  // 2^(E-21) / 16
-    if constexpr (VERIFY) {
+    if (verify) {
         // The sub-block sums are a function of the limbs: limbs and scale equal => table equal.
         bool diff = false;
 #pragma unroll
@@ -183,7 +181,7 @@ __device__ __forceinline__ bool convert_block(const float (&v)[8], uint8_t* xb, 
         }
         if (lane == 0) diff |= *reinterpret_cast<const uint32_t*>(xb + 800) != s16;
         return __any_sync(0xFFFFFFFFu, diff);
-    } else {
+    }
 #pragma unroll
     for (int n = 0; n < 3; ++n) {
         const int idx = (G & 1) * 6 + n * 2 + tlow;
@@ -206,29 +204,23 @@ __device__ __forceinline__ bool convert_block(const float (&v)[8], uint8_t* xb, 
     }
     if (lane == 0) *reinterpret_cast<uint32_t*>(xb + 800) = s16;
     return false;
-    }
 }
 
 // Super-blocks warp, warp + 9, ... of x are converted (or verified) by warp `warp` of the nine
-// working warps; the loads of four super-blocks are in flight at once.  Returns (VERIFY) whether
-// any of the warp's super-blocks no longer matches the table.
-template <bool VERIFY>
-__device__ __noinline__ bool convert_mine(const float* x, int bpr, int x_aligned, uint8_t* xtab, int warp, int lane) {
-    constexpr int kU = 4;
+// working warps, two at a time so that their loads overlap.  Returns (verify) whether any of the
+// warp's super-blocks no longer matches the table.
+__device__ __noinline__ bool convert_mine(const float* x, int bpr, int x_aligned, uint8_t* xtab, int warp, int lane,
+                                          bool verify) {
     constexpr int kWarps = kConsumerWarps + 1;
     bool diff = false;
-    for (int b0 = warp; b0 < bpr; b0 += kWarps * kU) {
-        float v[kU][8];
-#pragma unroll
-        for (int u = 0; u < kU; ++u) {
-            const int b = b0 + u * kWarps;
-            if (b < bpr) load8(v[u], x + (size_t)b * 256 + lane * 8, x_aligned);
-        }
-#pragma unroll
-        for (int u = 0; u < kU; ++u) {
-            const int b = b0 + u * kWarps;
-            if (b < bpr) diff |= convert_block<VERIFY>(v[u], xtab + (size_t)b * kXBlockBytes, lane);
-        }
+#pragma unroll 1
+    for (int b = warp; b < bpr; b += 2 * kWarps) {
+        float v0[8], v1[8];
+        const bool two = b + kWarps < bpr;
+        load8(v0, x + (size_t)b * 256 + lane * 8, x_aligned);
+        if (two) load8(v1, x + (size_t)(b + kWarps) * 256 + lane * 8, x_aligned);
+        diff |= convert_block(v0, xtab + (size_t)b * kXBlockBytes, lane, verify);
+        if (two) diff |= convert_block(v1, xtab + (size_t)(b + kWarps) * kXBlockBytes, lane, verify);
     }
     return diff;
 }
@@ -369,9 +361,9 @@ __device__ __forceinline__ int ld_volatile(const int* p) { return *reinterpret_c
 //                 share of x as soon as `released` is set, whatever it is doing.
 //   SPEC = false: x is final; results are stored directly.
 // Returns false when a bounded wait ran out.
-template <bool SPEC>
-__device__ __forceinline__ void run_pass(const Params& p, const CUtensorMap* wmap, Control* c, uint8_t* xtab,
-                                         float* partials, float* results, uint8_t* stages, int warp, int lane) {
+__device__ __forceinline__ void run_pass(const bool SPEC, const Params& p, const CUtensorMap* wmap, Control* c,
+                                         uint8_t* xtab, float* partials, float* results, uint8_t* stages, int warp,
+                                         int lane) {
     const int depth = p.depth;
     const int stage_bytes = kTileRows * p.row_stride;
     const int n_tiles = (p.rows + kTileRows - 1) / kTileRows;
@@ -384,7 +376,7 @@ __device__ __forceinline__ void run_pass(const Params& p, const CUtensorMap* wma
     // loop and every wait so that the verdict never waits for a warp that is busy or blocked.
     auto poll_verify = [&]() {
         if (verified || !ld_volatile(&c->released)) return;
-        const bool diff = convert_mine<true>(p.x, p.bpr, p.x_aligned, xtab, warp, lane);
+        const bool diff = convert_mine(p.x, p.bpr, p.x_aligned, xtab, warp, lane, true);
         if (lane == 0) {
             if (diff) atomicOr(&c->mismatch, 1);
             mbar_arrive(&c->verified_bar);
@@ -444,6 +436,7 @@ __device__ __forceinline__ void run_pass(const Params& p, const CUtensorMap* wma
             direct = true;
         };
         bool alive = true;
+#pragma unroll 1
         for (; u < total; ++u) {
             if (!wait_bar(c->done_bar + s, par)) {
                 alive = false;
@@ -509,6 +502,7 @@ __device__ __forceinline__ void run_pass(const Params& p, const CUtensorMap* wma
         float racc0 = 0.0f, racc1 = 0.0f;
         int win = 0, s = 0, pidx = 0, phase = 0;
         uint32_t par = 0;
+#pragma unroll 1
         for (int u = 0; u < total; ++u) {
             if (SPEC) {
                 poll_verify();
@@ -518,6 +512,7 @@ __device__ __forceinline__ void run_pass(const Params& p, const CUtensorMap* wma
             const int b0 = win * p.kb;
             const int nb = min(p.kb, p.bpr - b0);
             const uint8_t* stage = stages + (size_t)s * stage_bytes;
+#pragma unroll 1
             for (int i = (warp - phase - b0) & 7; i < nb; i += kConsumerWarps)
                 process_block(stage + i * q4k::kBlockBytes, p.row_stride, xtab + (size_t)(b0 + i) * kXBlockBytes, lc,
                               racc0, racc1);
@@ -590,13 +585,17 @@ matvec_q4k_mma_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) 
     }
     __syncthreads();
 
-    if (p.speculate) {
+    // Pass 0 (only with p.speculate): on x as it is NOW, while the kernel before this one may still
+    // run.  Pass 1: on the final x, when there was no speculation or it turned out stale.
+    bool spec = p.speculate != 0;
+#pragma unroll 1
+    for (int pass = 0; pass < 2; ++pass) {
+        if (!spec) griddep_wait();  // x may be produced by the kernel launched just before this one
         if (working) {
-            // x as it is NOW: the kernel before this one may still be running (and writing it)
-            convert_mine<false>(p.x, p.bpr, p.x_aligned, xtab, warp, lane);
+            convert_mine(p.x, p.bpr, p.x_aligned, xtab, warp, lane, false);
             asm volatile("bar.sync 1, %0;" ::"n"((kConsumerWarps + 1) * 32) : "memory");
-            run_pass<true>(p, &wmap, &ctl, xtab, partials, results, stages, warp, lane);
-        } else {
+            run_pass(spec, p, &wmap, &ctl, xtab, partials, results, stages, warp, lane);
+        } else if (spec) {
             griddep_wait();  // the kernel launched just before this one has completed
             if (lane == 0) {
                 __threadfence_block();
@@ -617,8 +616,9 @@ matvec_q4k_mma_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) 
                 *reinterpret_cast<volatile int*>(&ctl.verdict) = (ok && !ld_volatile(&ctl.mismatch)) ? kVerdictOk : kVerdictRedo;
             }
         }
+        if (!spec) break;
         __syncthreads();
-        if (ctl.verdict == kVerdictOk || ctl.abort) return;
+        if (ctl.verdict == kVerdictOk || ctl.abort) break;
         // x changed under the speculation: start over on the final x
         if (threadIdx.x == 0) {
             for (int s = 0; s < p.depth; ++s) {
@@ -629,13 +629,7 @@ matvec_q4k_mma_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) 
             init_barriers(&ctl, p.depth);
         }
         __syncthreads();
-    } else {
-        griddep_wait();  // x may be produced by the kernel launched just before this one
-    }
-    if (working) {
-        convert_mine<false>(p.x, p.bpr, p.x_aligned, xtab, warp, lane);
-        asm volatile("bar.sync 1, %0;" ::"n"((kConsumerWarps + 1) * 32) : "memory");
-        run_pass<false>(p, &wmap, &ctl, xtab, partials, results, stages, warp, lane);
+        spec = false;
     }
 }
 
@@ -661,10 +655,10 @@ int row_swap_for(int kb) {
     return -1;
 }
 
-// The ring that keeps the most weight bytes in flight inside `budget` bytes of shared memory.
+// The ring for rows of `bpr` super-blocks inside `budget` bytes of shared memory: the fewest windows
+// per tile (every stage use costs a round of barrier traffic), then the deepest ring that fits.
 bool pick_config(int bpr, int budget, int max_tiles, Config& best) {
     const int xtab = round128(bpr * kXBlockBytes);
-    long best_flight = -1;
     for (int n_win = (bpr + kMaxWindow - 1) / kMaxWindow; n_win <= bpr; ++n_win) {
         int kb = (bpr + n_win - 1) / n_win;
         if ((kb & 7) == 0) {  // widen the window by one if the split stays valid
@@ -678,15 +672,11 @@ bool pick_config(int bpr, int budget, int max_tiles, Config& best) {
         for (int depth = kMaxDepth; depth >= 3; --depth) {
             const int smem = xtab + round128(((depth + 1) * kConsumerWarps + max_tiles) * kTileRows * 4) + depth * stage;
             if (smem > budget) continue;
-            const long flight = (long)(depth - 1) * stage;
-            if (flight > best_flight) {
-                best_flight = flight;
-                best = Config{n_win, kb, depth, swap, smem};
-            }
-            break;
+            best = Config{n_win, kb, depth, swap, smem};
+            return true;
         }
     }
-    return best_flight >= 0;
+    return false;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -712,6 +702,13 @@ bool supported(int blocks_per_row) {
     return blocks_per_row > 0 && encode_tiled() != nullptr && pick_config(blocks_per_row, kSmemOnePerSm, 64, c);
 }
 
+bool fits_half_sm(int blocks_per_row) {
+    Config c;
+    // ... with whole rows in a stage: windows of longer rows cost a round of barrier traffic each
+    return blocks_per_row > 0 && encode_tiled() != nullptr && pick_config(blocks_per_row, kSmemTwoPerSm, 16, c) &&
+           c.n_win == 1;
+}
+
 cudaError_t launch(const uint8_t* w, const float* x, const float* addend, float* y, int rows, int bpr,
                    int hold_trigger, int speculate, unsigned* timeouts, int sms, cudaStream_t stream) {
     Config c;
@@ -720,19 +717,8 @@ cudaError_t launch(const uint8_t* w, const float* x, const float* addend, float*
     const int max_tiles = (n_tiles + grid - 1) / grid;
     // Half an SM when a useful ring fits beside the operand table (the successor kernel can then be
     // resident early); the whole SM for long rows.
-    const bool two = pick_config(bpr, kSmemTwoPerSm, max_tiles, c) && (long)(c.depth - 1) * kTileRows * c.kb * q4k::kBlockBytes >= 48 * 1024;
-    if (!two && !pick_config(bpr, kSmemOnePerSm, max_tiles, c)) return cudaErrorInvalidValue;
-    {   // BRING-UP override: MODGRAD_MMA_CFG="n_win,depth,budget_kb"
-        const char* e = getenv("MODGRAD_MMA_CFG");
-        int nw = 0, dp = 0, kb_ = 0;
-        if (e && sscanf(e, "%d,%d,%d", &nw, &dp, &kb_) == 3 && nw >= 1 && nw <= bpr && dp >= 2 && dp <= kMaxDepth) {
-            Config o;
-            o.n_win = nw; o.kb = (bpr + nw - 1) / nw; o.depth = dp;
-            o.row_swap = row_swap_for(o.kb);
-            o.smem = round128(bpr * kXBlockBytes) + round128(((dp + 1) * kConsumerWarps + max_tiles) * kTileRows * 4) + dp * kTileRows * o.kb * q4k::kBlockBytes;
-            if (o.smem <= kb_ * 1024 && o.row_swap >= 0 && o.kb <= kMaxWindow && (nw - 1) * o.kb < bpr) c = o;
-        }
-    }
+    if (!pick_config(bpr, kSmemTwoPerSm, max_tiles, c) && !pick_config(bpr, kSmemOnePerSm, max_tiles, c))
+        return cudaErrorInvalidValue;
     const EncodeTiledFn encode = encode_tiled();
     if (encode == nullptr) return cudaErrorNotSupported;
     // The weight matrix as a 2-D tensor of 8-byte elements: [rows][bpr * 18]; box = 16 rows x kb * 18.

@@ -7,6 +7,8 @@ namespace gemvmma {
 
 // Whether rows of `blocks_per_row` super-blocks fit the kernel's shared-memory operand table.
 bool supported(int blocks_per_row);
+// Whether the kernel needs only half an SM for such rows (two launches can then be resident together).
+bool fits_half_sm(int blocks_per_row);
 
 // y = dequant(w) . x + addend (addend may be null or alias y); asynchronous on `stream`, launched with
 // programmatic dependent launch.  `speculate`: convert x and start computing while the previous kernel of

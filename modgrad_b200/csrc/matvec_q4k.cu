@@ -333,6 +333,8 @@ cudaError_t workspace_for(cudaStream_t stream, size_t bytes, void** out) {
 // Above this many super-blocks per row the per-CTA conversion of x costs more than a separate
 // conversion kernel plus a scratch table.
 constexpr int kFusedConvertMaxBpr = 32;
+// From this many rows on (two or more 16-row tiles per SM) the tensor-core kernel wins.
+constexpr int kMmaMinRows = 4736;
 
 // Speculation of the tensor-core GEMV (gemv_q4k_mma.cu): it converts x and computes while the kernel
 // queued before it may still run, and publishes only after x has been re-checked.  A stale x costs
@@ -510,7 +512,14 @@ extern "C" int mg_matvec_q4k_bias_on_stream(const uint8_t* w_q4, const float* x,
     if (blocks_per_row > 0x7FFFFFFF / 256) return (int)cudaErrorInvalidValue;
     if (!peer_target_ok(peer, y, (size_t)out_dim * sizeof(float))) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
-    if (peer.world <= 1 && gemvmma::supported(blocks_per_row)) {
+    // Matrices of many short rows go to the tensor-core kernel (half an SM per CTA, speculative
+    // start: consecutive launches overlap); few rows or long rows are faster on the dp4a ring
+    // kernel below, whose x conversion is lighter.
+    static const int force_mma = [] { const char* e = getenv("MODGRAD_Q4K_GEMV_MMA"); return e ? atoi(e) : -1; }();
+    const bool want_mma = force_mma >= 0 ? force_mma != 0
+                                         : (out_dim >= kMmaMinRows && gemvmma::fits_half_sm(blocks_per_row)) ||
+                                               !limbs_path_ok(blocks_per_row);
+    if (peer.world <= 1 && want_mma && gemvmma::supported(blocks_per_row)) {
         // the tensor-core kernel: one launch, x converted inside, no scratch
         const mg::DeviceProps& dp = mg::device_props();
         unsigned* timeouts = nullptr;
