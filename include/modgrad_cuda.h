@@ -267,6 +267,57 @@ int mg_decoder_kernels_per_token(const mg_decoder* d);
  * peers; MODGRAD_DECODER_GATHER=nccl|peer|fused overrides); -1 on a single GPU. */
 int mg_decoder_gather_mode(const mg_decoder* d);
 
+/* The single device allocation that holds every weight tensor of the engine (the reference packs
+ * its quantised tensors the same way, crates/modgrad-gemma/src/rocm_gemma.rs:206-224) and the
+ * device pointer of one tensor inside it (`which` as for mg_decoder_upload). */
+void* mg_decoder_weight_arena(mg_decoder* d, size_t* bytes);
+void* mg_decoder_weight_ptr(mg_decoder* d, int layer, int which);
+
+/* ---- GGUF: header parser and checkpoint loader ---------------------------------------------------
+ * GgufFile::parse / TensorInfo / MetaValue / GgmlType::block_size of the reference
+ * (crates/modgrad-device/src/kfd/gguf.rs:11-234, :665-694): GGUF v2 and v3, little endian,
+ * metadata key/values of the thirteen value types (arrays nest), tensor infos, data section
+ * aligned to 32 bytes.  Only the header is decoded; the file is memory-mapped and tensor bytes are
+ * addressed by offset.  Return codes: 0, or -4 (Runtime) with the message in mg_gguf_last_error()
+ * ("not a GGUF file", "unsupported GGUF version N", "string too long", "unknown GGUF value type N",
+ * a short read).  Needs no GPU. */
+typedef struct mg_gguf mg_gguf;
+int mg_gguf_open(const char* path, mg_gguf** out);
+int mg_gguf_parse_memory(const void* data, size_t bytes, mg_gguf** out);
+void mg_gguf_close(mg_gguf* g);
+const char* mg_gguf_last_error(void);
+int mg_gguf_version(const mg_gguf* g);
+size_t mg_gguf_data_offset(const mg_gguf* g);
+int mg_gguf_n_tensors(const mg_gguf* g);
+int mg_gguf_n_meta(const mg_gguf* g);
+int mg_gguf_find_tensor(const mg_gguf* g, const char* name);
+/* dims4: dims[0] (the row length, in_dim) .. dims[3], 1 where absent; file_offset = data_offset + the
+ * tensor's offset (GgufFile::tensor_file_offset, gguf.rs:232-234). */
+int mg_gguf_tensor(const mg_gguf* g, int index, const char** name, int* n_dims, uint64_t* dims4, uint32_t* dtype,
+                   uint64_t* file_offset, uint64_t* data_bytes);
+const void* mg_gguf_tensor_data(const mg_gguf* g, int index);
+int mg_gguf_meta_u32(const mg_gguf* g, const char* key, uint32_t* out); /* U32, I32, U64: gguf.rs:117-124 */
+int mg_gguf_meta_f32(const mg_gguf* g, const char* key, float* out);    /* F32, F64: gguf.rs:125-131 */
+const char* mg_gguf_meta_str(const mg_gguf* g, const char* key);
+long long mg_gguf_meta_array_len(const mg_gguf* g, const char* key);
+void mg_gguf_block_size(uint32_t dtype, size_t* block_bytes, size_t* block_elems); /* gguf.rs:48-67 */
+
+/* LlmConfig::populate_from_gguf (crates/modgrad-device/src/kfd/llm.rs:145-180) and
+ * LlmWeights::load_from_gguf / RocmGemma::load (llm.rs:233-296; rocm_gemma.rs:94-262): engine
+ * configuration from the metadata, then every tensor uploaded verbatim from the mapped file into
+ * the engine's single weight allocation (rank `rank` of `world` uploads its row ranges only),
+ * behind a VRAM guard: weights + KV cache + activations plus a margin (512 MiB,
+ * MODGRAD_VRAM_MARGIN_MB) must fit the free device memory, else cudaErrorMemoryAllocation (2).
+ * Tensors: blk.N.{attn_q,attn_k,attn_v,attn_output,ffn_gate,ffn_up,ffn_down}.weight Q4_K,
+ * blk.N.{attn_norm,ffn_norm}.weight and output_norm.weight F32, token_embd.weight and
+ * output.weight F16 (LM head tied to the embedding when output.weight is absent, llm.rs:1281-1286).
+ * -4 with mg_decoder_load_error() for a malformed file, a missing tensor, a wrong shape or an
+ * unsupported tensor type. */
+int mg_decoder_config_from_gguf(const mg_gguf* g, int max_seq, mg_decoder_config* out);
+int mg_decoder_load_gguf(const char* path, int max_seq, int rank, int world, const void* nccl_id128,
+                         mg_decoder** out);
+const char* mg_decoder_load_error(void);
+
 /* ---- all-gather by direct peer stores over NVLink, fused into the producing kernel -----------
  * For row-sharded engines (one process per GPU of one box).  Every rank owns an `arena` of
  * device memory that the other ranks map with CUDA IPC; all ranks lay it out identically, the

@@ -96,6 +96,28 @@ SIGNATURES = {
     "mg_decoder_buffer": (vp, [vp, ci]),
     "mg_decoder_kernels_per_token": (ci, [vp]),
     "mg_decoder_gather_mode": (ci, [vp]),
+    "mg_decoder_weight_arena": (vp, [vp, C.POINTER(sz)]),
+    "mg_decoder_weight_ptr": (vp, [vp, ci, ci]),
+    "mg_gguf_open": (ci, [C.c_char_p, C.POINTER(vp)]),
+    "mg_gguf_parse_memory": (ci, [vp, sz, C.POINTER(vp)]),
+    "mg_gguf_close": (None, [vp]),
+    "mg_gguf_last_error": (C.c_char_p, []),
+    "mg_gguf_version": (ci, [vp]),
+    "mg_gguf_data_offset": (sz, [vp]),
+    "mg_gguf_n_tensors": (ci, [vp]),
+    "mg_gguf_n_meta": (ci, [vp]),
+    "mg_gguf_find_tensor": (ci, [vp, C.c_char_p]),
+    "mg_gguf_tensor": (ci, [vp, ci, C.POINTER(C.c_char_p), C.POINTER(ci), C.POINTER(C.c_uint64), C.POINTER(C.c_uint32),
+                             C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "mg_gguf_tensor_data": (vp, [vp, ci]),
+    "mg_gguf_meta_u32": (ci, [vp, C.c_char_p, C.POINTER(C.c_uint32)]),
+    "mg_gguf_meta_f32": (ci, [vp, C.c_char_p, C.POINTER(cf)]),
+    "mg_gguf_meta_str": (C.c_char_p, [vp, C.c_char_p]),
+    "mg_gguf_meta_array_len": (C.c_longlong, [vp, C.c_char_p]),
+    "mg_gguf_block_size": (None, [C.c_uint32, C.POINTER(sz), C.POINTER(sz)]),
+    "mg_decoder_config_from_gguf": (ci, [vp, ci, vp]),
+    "mg_decoder_load_gguf": (ci, [C.c_char_p, ci, ci, ci, vp, C.POINTER(vp)]),
+    "mg_decoder_load_error": (C.c_char_p, []),
     "mg_backend_create": (ci, [ci, C.POINTER(vp)]),
     "mg_backend_destroy": (None, [vp]),
     "mg_backend_name": (C.c_char_p, [vp]),

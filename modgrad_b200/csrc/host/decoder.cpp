@@ -49,6 +49,8 @@ struct Layer {
 struct mg_decoder {
     mg_decoder_config cfg{};
     std::vector<Layer> layers;
+    uint8_t* weights = nullptr;  // the one allocation that holds every weight tensor
+    size_t weights_bytes = 0;
     __half *embed = nullptr, *lm_head = nullptr;
     float* out_norm = nullptr;
     float* rope_freq = nullptr;  // base^(-2i/head_dim), i < head_dim/2
@@ -497,22 +499,43 @@ int mg_decoder_create_sharded(const mg_decoder_config* cfg, int rank, int world,
     const int D = c.d_model, F = c.d_ff, hd = c.head_dim, q_dim = c.n_heads * hd;
     const int q_loc = (d->h1 - d->h0) * hd, kv_loc = (d->kv1 - d->kv0) * hd;
     d->layers.resize(c.n_layers);
+    {   // Every weight lives in ONE device allocation addressed by offset, as the reference's engine
+        // packs its quantised tensors (crates/modgrad-gemma/src/rocm_gemma.rs:206-224); 256-byte
+        // aligned sub-ranges, so every Q4_K row stays 16-byte aligned.
+        size_t off = 0;
+        auto take = [&](size_t bytes) {
+            const size_t at = off;
+            off += (bytes + 255) & ~(size_t)255;
+            return at;
+        };
+        struct Slots { size_t wq, wk, wv, wo, wgate, wup, wdown, attn_norm, ffn_norm; };
+        std::vector<Slots> slots(c.n_layers);
+        for (Slots& sl : slots) {
+            sl.wq = take(q4k_bytes(q_loc, D)); sl.wk = take(q4k_bytes(kv_loc, D)); sl.wv = take(q4k_bytes(kv_loc, D));
+            sl.wo = take(q4k_bytes(d->d_loc, q_dim)); sl.wgate = take(q4k_bytes(d->f_loc, D));
+            sl.wup = take(q4k_bytes(d->f_loc, D)); sl.wdown = take(q4k_bytes(d->d_loc, F));
+            sl.attn_norm = take((size_t)D * 4); sl.ffn_norm = take((size_t)D * 4);
+        }
+        const size_t o_embed = take((size_t)c.vocab * D * 2), o_head = take((size_t)d->v_loc * D * 2),
+                     o_norm = take((size_t)D * 4);
+        if ((rc = dev_alloc(d, &d->weights, off))) return bail(rc);
+        d->weights_bytes = off;
+        for (int l = 0; l < c.n_layers; ++l) {
+            Layer& L = d->layers[l];
+            const Slots& sl = slots[l];
+            L.wq = d->weights + sl.wq; L.wk = d->weights + sl.wk; L.wv = d->weights + sl.wv; L.wo = d->weights + sl.wo;
+            L.wgate = d->weights + sl.wgate; L.wup = d->weights + sl.wup; L.wdown = d->weights + sl.wdown;
+            L.attn_norm = reinterpret_cast<float*>(d->weights + sl.attn_norm);
+            L.ffn_norm = reinterpret_cast<float*>(d->weights + sl.ffn_norm);
+        }
+        d->embed = reinterpret_cast<__half*>(d->weights + o_embed);
+        d->lm_head = reinterpret_cast<__half*>(d->weights + o_head);
+        d->out_norm = reinterpret_cast<float*>(d->weights + o_norm);
+    }
     for (Layer& L : d->layers) {
-        if ((rc = dev_alloc(d, &L.wq, q4k_bytes(q_loc, D)))) return bail(rc);
-        if ((rc = dev_alloc(d, &L.wk, q4k_bytes(kv_loc, D)))) return bail(rc);
-        if ((rc = dev_alloc(d, &L.wv, q4k_bytes(kv_loc, D)))) return bail(rc);
-        if ((rc = dev_alloc(d, &L.wo, q4k_bytes(d->d_loc, q_dim)))) return bail(rc);
-        if ((rc = dev_alloc(d, &L.wgate, q4k_bytes(d->f_loc, D)))) return bail(rc);
-        if ((rc = dev_alloc(d, &L.wup, q4k_bytes(d->f_loc, D)))) return bail(rc);
-        if ((rc = dev_alloc(d, &L.wdown, q4k_bytes(d->d_loc, F)))) return bail(rc);
-        if ((rc = dev_alloc(d, &L.attn_norm, (size_t)D))) return bail(rc);
-        if ((rc = dev_alloc(d, &L.ffn_norm, (size_t)D))) return bail(rc);
         if ((rc = dev_alloc(d, &L.k_cache, (size_t)c.max_seq * kv_loc))) return bail(rc);
         if ((rc = dev_alloc(d, &L.v_cache, (size_t)c.max_seq * kv_loc))) return bail(rc);
     }
-    if ((rc = dev_alloc(d, &d->embed, (size_t)c.vocab * D))) return bail(rc);
-    if ((rc = dev_alloc(d, &d->lm_head, (size_t)d->v_loc * D))) return bail(rc);
-    if ((rc = dev_alloc(d, &d->out_norm, (size_t)D))) return bail(rc);
     if ((rc = dev_alloc(d, &d->cur, (size_t)D))) return bail(rc);
     if ((rc = dev_alloc(d, &d->q, (size_t)q_loc))) return bail(rc);
     if ((rc = dev_alloc(d, &d->k, (size_t)kv_loc))) return bail(rc);
@@ -771,6 +794,39 @@ void* mg_decoder_buffer(mg_decoder* d, int which) {
         case 2: return d->state;
         case 3: return d->pair_buf;
         case 4: return static_cast<char*>(d->argmax_scratch) + 2048;
+        default: return nullptr;
+    }
+}
+// Base and size of the single device allocation that holds all weights (offsets of the tensors
+// inside it follow from mg_decoder_weight_ptr).
+void* mg_decoder_weight_arena(mg_decoder* d, size_t* bytes) {
+    if (!d) return nullptr;
+    if (bytes) *bytes = d->weights_bytes;
+    return d->weights;
+}
+// Device pointer of one weight tensor (the `which` codes of mg_decoder_upload).
+void* mg_decoder_weight_ptr(mg_decoder* d, int layer, int which) {
+    if (!d) return nullptr;
+    if (which >= MG_W_EMBED) {
+        switch (which) {
+            case MG_W_EMBED: return d->embed;
+            case MG_W_LM_HEAD: return d->lm_head;
+            case MG_W_OUT_NORM: return d->out_norm;
+            default: return nullptr;
+        }
+    }
+    if (layer < 0 || layer >= d->cfg.n_layers) return nullptr;
+    Layer& L = d->layers[layer];
+    switch (which) {
+        case MG_W_Q: return L.wq;
+        case MG_W_K: return L.wk;
+        case MG_W_V: return L.wv;
+        case MG_W_O: return L.wo;
+        case MG_W_GATE: return L.wgate;
+        case MG_W_UP: return L.wup;
+        case MG_W_DOWN: return L.wdown;
+        case MG_W_ATTN_NORM: return L.attn_norm;
+        case MG_W_FFN_NORM: return L.ffn_norm;
         default: return nullptr;
     }
 }

@@ -118,6 +118,41 @@ class Q4KDecoder:
             raise Runtime(f"mg_decoder_create: {self._lib.mg_get_error_string(code).decode()}")
         self._h = h.value
 
+    @classmethod
+    def from_gguf(cls, path: str, max_seq: int, rank: int = 0, world: int = 1, nccl_id: bytes | None = None):
+        """``RocmGemma::load``: configuration from the file's metadata, every tensor uploaded verbatim
+        from the memory-mapped file (this rank's row ranges), behind the VRAM guard."""
+        from . import gguf
+        lib = _lib.load()
+        with gguf.GgufFile.open(path) as g:
+            cs = DecoderConfigC()
+            if lib.mg_decoder_config_from_gguf(g.handle, max_seq, C.byref(cs)) != 0:
+                raise Runtime(f"gguf config: {lib.mg_decoder_load_error().decode()}")
+        cfg = DecoderConfig(cs.n_layers, cs.d_model, cs.n_heads, cs.n_kv_heads, cs.head_dim, cs.d_ff, cs.vocab,
+                            cs.max_seq, cs.rms_eps, cs.rope_base)
+        self = cls.__new__(cls)
+        self.cfg = cfg
+        self.shard = shard_mod.decoder_shard(cfg, rank, world)
+        self._lib = lib
+        h = C.c_void_p()
+        idbuf = C.create_string_buffer(nccl_id, 128) if nccl_id is not None else None
+        code = lib.mg_decoder_load_gguf(str(path).encode(), max_seq, rank, world, idbuf, C.byref(h))
+        if code != 0 or not h.value:
+            from .backend import OutOfMemory
+            msg = lib.mg_decoder_load_error().decode()
+            raise (OutOfMemory if code == 2 else Runtime)(f"load_gguf: {msg}")
+        self._h = h.value
+        self.set_position(0)
+        return self
+
+    def weight_arena(self) -> tuple[int, int]:
+        """(base device pointer, bytes) of the single allocation that holds every weight tensor."""
+        n = C.c_size_t()
+        return int(self._lib.mg_decoder_weight_arena(self._h, C.byref(n)) or 0), n.value
+
+    def weight_ptr(self, layer: int, which: int) -> int:
+        return int(self._lib.mg_decoder_weight_ptr(self._h, layer, which) or 0)
+
     def close(self):
         if getattr(self, "_h", None):
             self._lib.mg_decoder_destroy(self._h)

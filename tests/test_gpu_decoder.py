@@ -231,6 +231,36 @@ def test_decoder_logits_match_oracle_teacher_forced(orc, monkeypatch, persistent
     d.close()
 
 
+def test_decoder_full_size_7b_logits_match_oracle(orc):
+    """The 7B-class configuration itself (28 layers, 3584 / 18944, 28/4 heads of 128, vocabulary
+    152064, 2048-position half KV prefill): two teacher-forced tokens against the oracle's
+    forward_token on the same host tensors."""
+    cfg, seed, prefill = dec.QWEN25_7B, 5, 2048
+    d = dec.Q4KDecoder(cfg)
+    keep, layers = [], []
+    p = lambda a: a.ctypes.data_as(C.c_void_p)
+
+    def on_layer(l, lw):
+        kc = np.zeros(cfg.max_seq * cfg.kv_dim, dtype=np.float16)
+        vc = np.zeros_like(kc)
+        k, v = dec.kv_prefill(cfg, l, prefill, seed)
+        kc[:k.size], vc[:v.size] = k, v
+        keep.append((lw, kc, vc))
+        layers.append(DecoderLayer(p(lw["wq"]), p(lw["wk"]), p(lw["wv"]), p(lw["wo"]), p(lw["wgate"]), p(lw["wup"]),
+                                   p(lw["wdown"]), p(lw["attn_norm"]), p(lw["ffn_norm"]), p(kc), p(vc)))
+
+    g = d.load_random(seed, prefill=prefill, on_layer=on_layer)
+    ccfg = DecoderCfg(cfg.n_layers, cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.d_ff, cfg.vocab,
+                      cfg.max_seq, cfg.rms_eps, cfg.rope_base)
+    for step, tok in enumerate([151000, 42]):
+        want = orc.forward_token(ccfg, layers, g["embed"], g["lm_head"], g["out_norm"], prefill + step, tok, MODE_F64)
+        got, nxt = d.forward_token(tok)
+        err = rel_rms_err(got, want)
+        assert err < DECODER_TOL, (step, err)
+        assert nxt == orc.argmax(got)
+    d.close()
+
+
 def test_decoder_generate_is_greedy_feedback(orc):
     cfg, seed = SMALL, 11
     d = dec.Q4KDecoder(cfg)
