@@ -80,6 +80,30 @@ int launch_matvec_q4k_dp4a(const uint8_t* w, const int8_t* xq, const float* xd, 
 int launch_matvec_q4k_dp4a_on_stream(const uint8_t* w, const int8_t* xq, const float* xd, const float* xsum,
                                      float* y, int out_dim, int bpr, void* stream);
 
+/* The other two K-quant formats of real GGUF checkpoints, same launcher ABI as Q4_K:
+ * launch_matvec_q5k replaces crates/modgrad-device/kernels/matvec_q5k.hip:112-121 (Rust declaration
+ * rocm.rs:466-472; weight out_dim*blocks_per_row*176 bytes, 16-byte aligned), launch_matvec_q6k
+ * replaces matvec_q6k.hip:85-94 (rocm.rs:481-484; 210-byte blocks, 2-byte aligned),
+ * launch_matvec_q6k_dp4a replaces matvec_q6k_dp4a.hip:139-150 (rocm.rs:489-490; int8 activations
+ * from launch_quantize_q8_1, lossy; xsum is unused: Q6_K has no per-block minimum).  f32 results
+ * within 1e-5 of the output RMS of an f64-accumulated dot of the host dequantiser's weights
+ * (crates/modgrad-device/src/kfd/gguf.rs:421-455, :458-484). */
+int launch_matvec_q5k(const uint8_t* w_q5, const float* x, float* y, int out_dim, int blocks_per_row);
+int launch_matvec_q5k_on_stream(const uint8_t* w_q5, const float* x, float* y, int out_dim, int blocks_per_row,
+                                void* stream);
+int launch_matvec_q6k(const uint8_t* w_q6, const float* x, float* y, int out_dim, int blocks_per_row);
+int launch_matvec_q6k_on_stream(const uint8_t* w_q6, const float* x, float* y, int out_dim, int blocks_per_row,
+                                void* stream);
+int launch_matvec_q6k_dp4a(const uint8_t* w, const int8_t* xq, const float* xd, const float* xsum, float* y,
+                           int out_dim, int bpr);
+int launch_matvec_q6k_dp4a_on_stream(const uint8_t* w, const int8_t* xq, const float* xd, const float* xsum,
+                                     float* y, int out_dim, int bpr, void* stream);
+/* Bulk dequantisation on the device, bit-exact against the host dequantisers (gguf.rs:421-455,
+ * :458-484); the reference has no device kernel for these (it dequantises Q5_K / Q6_K rows on the
+ * host, e.g. one embedding row per token, rocm_gemma.rs:316-323). */
+int mg_dequant_q5k_on_stream(const uint8_t* q5k, int n_blocks, float* fp32_out, void* stream);
+int mg_dequant_q6k_on_stream(const uint8_t* q6k, int n_blocks, float* fp32_out, void* stream);
+
 /* y = dequant(w_q4) . x + bias, bias may be NULL.  The semantics of Op::Matvec{quant: Q4K}
  * (crates/modgrad-device/src/backend/op.rs:175-186) and of the KFD kernel's kernarg block
  * (crates/modgrad-device/src/kfd/dispatch_queue.rs:235-262); the HIP launcher has no bias. */

@@ -34,6 +34,14 @@ SIGNATURES = {
     "launch_quantize_q8_1_on_stream": (ci, [vp, vp, vp, vp, ci, vp]),
     "launch_matvec_q4k_dp4a": (ci, [vp, vp, vp, vp, vp, ci, ci]),
     "launch_matvec_q4k_dp4a_on_stream": (ci, [vp, vp, vp, vp, vp, ci, ci, vp]),
+    "launch_matvec_q5k": (ci, [vp, vp, vp, ci, ci]),
+    "launch_matvec_q5k_on_stream": (ci, [vp, vp, vp, ci, ci, vp]),
+    "launch_matvec_q6k": (ci, [vp, vp, vp, ci, ci]),
+    "launch_matvec_q6k_on_stream": (ci, [vp, vp, vp, ci, ci, vp]),
+    "launch_matvec_q6k_dp4a": (ci, [vp, vp, vp, vp, vp, ci, ci]),
+    "launch_matvec_q6k_dp4a_on_stream": (ci, [vp, vp, vp, vp, vp, ci, ci, vp]),
+    "mg_dequant_q5k_on_stream": (ci, [vp, ci, vp, vp]),
+    "mg_dequant_q6k_on_stream": (ci, [vp, ci, vp, vp]),
     "launch_dequant_q4k": (ci, [vp, ci, vp]),
     "launch_dequant_q4k_on_stream": (ci, [vp, ci, vp, vp]),
     "mg_matvec_q4k_bias_on_stream": (ci, [vp, vp, vp, vp, ci, ci, vp]),

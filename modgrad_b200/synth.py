@@ -43,6 +43,38 @@ def q4k_blocks(n_blocks: int, rng: np.random.Generator) -> np.ndarray:
     return out
 
 
+def q5k_blocks(n_blocks: int, rng: np.random.Generator) -> np.ndarray:
+    """Random Q5_K super-blocks (176 bytes: d, dmin, scales[12], qh[32], ql[128];
+    crates/modgrad-device/src/kfd/gguf.rs:421-432), same distributions as the Q4_K generator."""
+    out = np.empty((n_blocks, 176), dtype=np.uint8)
+    dd = (np.abs(rng.standard_normal((n_blocks, 2), dtype=np.float32)) * np.float32(0.01)).astype(np.float16)
+    out[:, 0:4] = dd.view(np.uint8).reshape(n_blocks, 4)
+    sc = rng.integers(0, 64, size=(n_blocks, 8), dtype=np.uint8)
+    m = rng.integers(0, 64, size=(n_blocks, 8), dtype=np.uint8)
+    out[:, 4:16] = pack_scales_mins(sc, m)
+    out[:, 16:176] = rng.integers(0, 256, size=(n_blocks, 160), dtype=np.uint8)
+    return out
+
+
+def q6k_blocks(n_blocks: int, rng: np.random.Generator) -> np.ndarray:
+    """Random Q6_K super-blocks (210 bytes: ql[128], qh[64], 16 signed scales, d;
+    crates/modgrad-device/src/kfd/gguf.rs:458-466): quants uniform, scales uniform in [-128, 127],
+    d = half(|N(0,1)| * 0.001)."""
+    out = np.empty((n_blocks, 210), dtype=np.uint8)
+    out[:, 0:208] = rng.integers(0, 256, size=(n_blocks, 208), dtype=np.uint8)
+    d = (np.abs(rng.standard_normal((n_blocks, 1), dtype=np.float32)) * np.float32(0.001)).astype(np.float16)
+    out[:, 208:210] = d.view(np.uint8).reshape(n_blocks, 2)
+    return out
+
+
+def kquant_matrix(kind: int, out_dim: int, in_dim: int, seed) -> np.ndarray:
+    """Row-major Q5_K (kind 5) or Q6_K (kind 6) weight as a flat uint8 array."""
+    assert in_dim % BLOCK_ELEMS == 0
+    rng = seed if isinstance(seed, np.random.Generator) else np.random.Generator(np.random.PCG64(seed))
+    gen = {5: q5k_blocks, 6: q6k_blocks}[kind]
+    return gen(out_dim * (in_dim // BLOCK_ELEMS), rng).reshape(-1)
+
+
 def q4k_matrix(out_dim: int, in_dim: int, seed) -> np.ndarray:
     """Row-major Q4_K weight ``[out_dim][in_dim/256][144]`` as a flat uint8 array."""
     assert in_dim % BLOCK_ELEMS == 0

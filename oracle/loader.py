@@ -19,7 +19,7 @@ MODE_SCALAR, MODE_SELECT, MODE_F64 = 0, 1, 2
 
 def build(force: bool = False) -> Path:
     """Compile the oracle with the committed Makefile (gcc, -ffp-contract=off)."""
-    srcs = [_HERE / "q4k_oracle.c", _HERE / "decoder_oracle.c", _HERE / "Makefile"]
+    srcs = [_HERE / "q4k_oracle.c", _HERE / "decoder_oracle.c", _HERE / "kquant_oracle.c", _HERE / "Makefile"]
     stale = (not _SO.exists()) or any(s.stat().st_mtime > _SO.stat().st_mtime for s in srcs)
     if force or stale:
         subprocess.run(["make", "-C", str(_HERE), "-B" if force else "-s"], check=True,
@@ -63,6 +63,10 @@ class OracleLib:
         c.orc_matvec_q4k_f64.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
         c.orc_quantize_q8_1.argtypes = [C.c_void_p] * 4 + [C.c_int]
         c.orc_matvec_q4k_q8_1.argtypes = [C.c_void_p] * 5 + [C.c_int, C.c_int]
+        c.orc_dequantize_row_q5_k.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        c.orc_dequantize_row_q6_k.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        c.orc_matvec_kquant_f64.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+        c.orc_matvec_q6k_q8_1.argtypes = [C.c_void_p] * 4 + [C.c_int, C.c_int]
         c.orc_rms_norm.argtypes = [C.c_void_p] * 3 + [C.c_int, C.c_float]
         c.orc_apply_rope.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float]
         c.orc_attention_f16kv.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4
@@ -88,6 +92,30 @@ class OracleLib:
         out = np.empty(n * 256, dtype=np.float32)
         self.c.orc_dequantize_row_q4_k(_p(b), _p(out), n)
         return out
+
+    def dequantize_kquant(self, kind: int, blocks: np.ndarray) -> np.ndarray:
+        """kind 5: Q5_K (176-byte blocks), 6: Q6_K (210-byte blocks)."""
+        bb = {5: 176, 6: 210}[kind]
+        b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+        n = b.size // bb
+        out = np.empty(n * 256, dtype=np.float32)
+        (self.c.orc_dequantize_row_q5_k if kind == 5 else self.c.orc_dequantize_row_q6_k)(_p(b), _p(out), n)
+        return out
+
+    def matvec_kquant_f64(self, kind: int, w: np.ndarray, x: np.ndarray, out_dim: int, bpr: int) -> np.ndarray:
+        bb = {5: 176, 6: 210}[kind]
+        w = np.ascontiguousarray(w, dtype=np.uint8).reshape(-1)
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        assert w.size == out_dim * bpr * bb and x.size >= bpr * 256
+        y = np.empty(out_dim, dtype=np.float64)
+        self.c.orc_matvec_kquant_f64(kind, _p(w), _p(x), _p(y), out_dim, bpr)
+        return y
+
+    def matvec_q6k_q8_1(self, w, xq, xd, out_dim, bpr):
+        w = np.ascontiguousarray(w, dtype=np.uint8).reshape(-1)
+        y = np.empty(out_dim, dtype=np.float32)
+        self.c.orc_matvec_q6k_q8_1(_p(w), _p(xq), _p(xd), _p(y), out_dim, bpr)
+        return y
 
     # ---- matvec -----------------------------------------------------------------------
     def matvec(self, w: np.ndarray, x: np.ndarray, out_dim: int, bpr: int, mode: int = MODE_F64,

@@ -76,3 +76,53 @@ def dequantize(blocks: np.ndarray) -> np.ndarray:
 def matvec_f64(w_blocks: np.ndarray, x: np.ndarray, out_dim: int, bpr: int) -> np.ndarray:
     w = dequantize(w_blocks).reshape(out_dim, bpr * BLOCK_ELEMS).astype(np.float64)
     return w @ np.asarray(x, dtype=np.float32)[: bpr * BLOCK_ELEMS].astype(np.float64)
+
+
+# ---- Q5_K / Q6_K (independent restatements, vectorised differently from the C oracle) ------------
+def half_bits_to_f32_zero_nonfinite(h: np.ndarray) -> np.ndarray:
+    v = f16_to_f32(h)
+    return np.where(np.isfinite(v), v, np.float32(0)).astype(np.float32)
+
+
+def unpack_scales_mins(scales: np.ndarray):
+    return scale_min_k4(scales)
+
+
+def dequantize_q5k(blocks: np.ndarray) -> np.ndarray:
+    """crates/modgrad-device/src/kfd/gguf.rs:421-455, all blocks at once."""
+    b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1, 176)
+    n = b.shape[0]
+    d = half_bits_to_f32_zero_nonfinite(b[:, 0:2].copy().view(np.uint16).reshape(n))
+    dmin = half_bits_to_f32_zero_nonfinite(b[:, 2:4].copy().view(np.uint16).reshape(n))
+    sc, m = unpack_scales_mins(b[:, 4:16])
+    qh, ql = b[:, 16:48], b[:, 48:176].reshape(n, 4, 32)
+    out = np.empty((n, 8, 32), dtype=np.float32)
+    for g in range(4):
+        for hi in range(2):
+            s = 2 * g + hi
+            nib = (ql[:, g] >> 4) if hi else (ql[:, g] & 0xF)
+            hbit = ((qh >> s) & 1).astype(np.uint8) * 16
+            q = (nib + hbit).astype(np.float32)
+            d1 = (d * sc[:, s].astype(np.float32)).astype(np.float32)
+            m1 = (dmin * m[:, s].astype(np.float32)).astype(np.float32)
+            out[:, s] = ((d1[:, None] * q).astype(np.float32) - m1[:, None]).astype(np.float32)
+    return out.reshape(-1)
+
+
+def dequantize_q6k(blocks: np.ndarray) -> np.ndarray:
+    """crates/modgrad-device/src/kfd/gguf.rs:458-484, all blocks at once."""
+    b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1, 210)
+    n = b.shape[0]
+    ql, qh = b[:, 0:128].reshape(n, 2, 64), b[:, 128:192].reshape(n, 2, 32)
+    sc = b[:, 192:208].copy().view(np.int8).reshape(n, 2, 8).astype(np.float32)
+    d = half_bits_to_f32_zero_nonfinite(b[:, 208:210].copy().view(np.uint16).reshape(n))
+    out = np.empty((n, 2, 4, 32), dtype=np.float32)
+    for k in range(4):  # q1..q4: low/high nibble of ql[l] / ql[l+32], two bits of qh at 2k
+        src = ql[:, :, (k & 1) * 32:(k & 1) * 32 + 32]
+        nib = (src >> 4) if k >= 2 else (src & 0xF)
+        q = (nib.astype(np.int32) | (((qh >> (2 * k)) & 3).astype(np.int32) << 4)) - 32
+        s = np.stack([sc[:, :, 2 * k], sc[:, :, 2 * k + 1]], axis=-1)        # scale of l < 16, l >= 16
+        s = np.repeat(s, 16, axis=-1)                                         # (n, 2, 32)
+        ds = (d[:, None, None] * s).astype(np.float32)
+        out[:, :, k] = (ds * q.astype(np.float32)).astype(np.float32)
+    return out.reshape(-1)

@@ -151,3 +151,26 @@ def test_gemv_bytes_formula():
 
 def test_tolerance_constant():
     assert GEMV_TOL == 1e-5
+
+
+def test_kquant_oracle_matches_kats_and_numpy(orc):
+    """Q5_K / Q6_K: the C restatement against the format-derived known-answer blocks (bit-exact)
+    and against the independent numpy restatement on random blocks and special scales."""
+    import json
+    from conftest import GOLDEN
+    from oracle import q4k_numpy as qn
+    for k in json.loads((GOLDEN / "kquant_kats.json").read_text())["kats"]:
+        blk = np.frombuffer(bytes.fromhex(k["block_hex"]), dtype=np.uint8)
+        want = np.array(k["expected_f32_bits"], dtype=np.uint32)
+        assert np.array_equal(orc.dequantize_kquant(k["kind"], blk).view(np.uint32), want), k["name"]
+    rng = np.random.Generator(np.random.PCG64(12))
+    for kind, gen, fn in ((5, synth.q5k_blocks, qn.dequantize_q5k), (6, synth.q6k_blocks, qn.dequantize_q6k)):
+        b = gen(3000, rng)
+        off = 0 if kind == 5 else 208
+        b[0, off:off + 2], b[1, off:off + 2], b[2, off:off + 2] = [0, 0x7C], [1, 0x7E], [1, 0]
+        assert np.array_equal(orc.dequantize_kquant(kind, b).view(np.uint32), fn(b).view(np.uint32))
+        w = gen(4 * 3, rng).reshape(-1)
+        x = synth.activations(3 * 256, rng)
+        y = orc.matvec_kquant_f64(kind, w, x, 4, 3)
+        ref = fn(w).reshape(4, -1).astype(np.float64) @ x.astype(np.float64)
+        assert np.allclose(y, ref, rtol=1e-12, atol=1e-12)
