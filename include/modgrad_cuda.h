@@ -297,6 +297,33 @@ int mg_decoder_gather_mode(const mg_decoder* d);
 void* mg_decoder_weight_arena(mg_decoder* d, size_t* bytes);
 void* mg_decoder_weight_ptr(mg_decoder* d, int layer, int which);
 
+/* ---- Q4_K residency: LinearResidentQuantized (crates/modgrad-compute/src/neuron.rs:866-1250) ------
+ * The weight lives on the host as Q4_K super-blocks; device buffers exist between ensure_resident
+ * and evict.  Default forward: the matvec runs on the Q4_K bytes themselves (launch_matvec_q4k +
+ * bias; 0.5625 bytes per weight).  mg_linear_q4k_set_expanded(l, 1) selects the reference's
+ * behaviour: dequantise once per residency into an fp32 copy (Op::DequantQ4KResident) and run a
+ * dense fp32 matvec (7x the memory and traffic).  from_* allocate nothing on the device; an evict
+ * followed by a forward reproduces the previous output bit for bit.  -4: bad arguments or
+ * in_dim % 256 != 0; positive: CUDA error codes.  mg_quantize_row_q4_k is the host quantiser
+ * (canonical ggml element order, the one dequantize_row_q4_k reads, gguf.rs:364-404). */
+typedef struct mg_linear_q4k mg_linear_q4k;
+int mg_quantize_row_q4_k(const float* x, uint8_t* out, size_t n);
+int mg_linear_q4k_from_f32(const float* weight, const float* bias, int in_dim, int out_dim, mg_linear_q4k** out);
+int mg_linear_q4k_from_blocks(const uint8_t* q4k, const float* bias, int in_dim, int out_dim, mg_linear_q4k** out);
+void mg_linear_q4k_destroy(mg_linear_q4k* l);
+int mg_linear_q4k_set_expanded(mg_linear_q4k* l, int expanded);
+int mg_linear_q4k_is_resident(const mg_linear_q4k* l);
+size_t mg_linear_q4k_host_size_bytes(const mg_linear_q4k* l);
+size_t mg_linear_q4k_device_size_bytes(const mg_linear_q4k* l);
+const uint8_t* mg_linear_q4k_host_blocks(const mg_linear_q4k* l, size_t* bytes);
+int mg_linear_q4k_ensure_resident(mg_linear_q4k* l, void* stream);
+void mg_linear_q4k_evict(mg_linear_q4k* l);
+int mg_linear_q4k_forward(mg_linear_q4k* l, const float* x_dev, float* out_dev, int auto_evict, void* stream);
+/* Dense fp32 matvec y = W[out_dim][in_dim] . x + bias (bias may be NULL): what the expanded mode
+ * dispatches (ops::matvec_resident -> hipblasSgemv in the reference, neuron.rs:1093-1101). */
+int mg_matvec_f32_on_stream(const float* w, const float* x, const float* bias, float* y, int out_dim, int in_dim,
+                            void* stream);
+
 /* ---- GGUF: header parser and checkpoint loader ---------------------------------------------------
  * GgufFile::parse / TensorInfo / MetaValue / GgmlType::block_size of the reference
  * (crates/modgrad-device/src/kfd/gguf.rs:11-234, :665-694): GGUF v2 and v3, little endian,

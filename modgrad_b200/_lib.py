@@ -106,6 +106,19 @@ SIGNATURES = {
     "mg_decoder_gather_mode": (ci, [vp]),
     "mg_decoder_weight_arena": (vp, [vp, C.POINTER(sz)]),
     "mg_decoder_weight_ptr": (vp, [vp, ci, ci]),
+    "mg_quantize_row_q4_k": (ci, [vp, vp, sz]),
+    "mg_linear_q4k_from_f32": (ci, [vp, vp, ci, ci, C.POINTER(vp)]),
+    "mg_linear_q4k_from_blocks": (ci, [vp, vp, ci, ci, C.POINTER(vp)]),
+    "mg_linear_q4k_destroy": (None, [vp]),
+    "mg_linear_q4k_set_expanded": (ci, [vp, ci]),
+    "mg_linear_q4k_is_resident": (ci, [vp]),
+    "mg_linear_q4k_host_size_bytes": (sz, [vp]),
+    "mg_linear_q4k_device_size_bytes": (sz, [vp]),
+    "mg_linear_q4k_host_blocks": (vp, [vp, C.POINTER(sz)]),
+    "mg_linear_q4k_ensure_resident": (ci, [vp, vp]),
+    "mg_linear_q4k_evict": (None, [vp]),
+    "mg_linear_q4k_forward": (ci, [vp, vp, vp, ci, vp]),
+    "mg_matvec_f32_on_stream": (ci, [vp, vp, vp, vp, ci, ci, vp]),
     "mg_gguf_open": (ci, [C.c_char_p, C.POINTER(vp)]),
     "mg_gguf_parse_memory": (ci, [vp, sz, C.POINTER(vp)]),
     "mg_gguf_close": (None, [vp]),
