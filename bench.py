@@ -671,7 +671,9 @@ def decode_leg_sharded(args, rank, world):
            "parallelism": f"rows sharded over {world} GPUs, head-parallel attention, all-gather of slices: "
                           + {"nccl": "NCCL collectives in the token graph",
                              "peer": "one peer-store gather kernel per collective (NVLink)",
-                             "fused": "peer stores over NVLink fused into the producing kernels"}[d.gather_mode()],
+                             "fused": "peer stores over NVLink fused into the producing kernels, flag handshake at their end",
+                             "stamped": "peer stores over NVLink fused into the producing kernels, every word stamped "
+                                        "with its epoch (no handshake; the consuming kernel polls)"}[d.gather_mode()],
            "gather": d.gather_mode(),
            "model": "qwen2.5-7b-shaped, random-init, Q4_K linears"}
     d.close()

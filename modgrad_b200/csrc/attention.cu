@@ -231,7 +231,11 @@ __global__ void __launch_bounds__(128) sdpa_merge_kernel(const float* partial,
     for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
         float acc = 0.0f;
         for (int s = 0; s < n_splits; ++s) acc = fmaf(p[(size_t)s * stride + 2 + d], f[s], acc);
-        if (peer.world > 1) mgpeer::store_all(peer, out + (size_t)h * head_dim + d, acc / L);
+        if (peer.world > 1 && peer.stamp_slots != nullptr) {
+            out[(size_t)h * head_dim + d] = acc / L;
+            mgpeer::store_stamped_all(peer, (long long)h * head_dim + d, __float_as_uint(acc / L),
+                                      mgpeer::exchange_epoch(peer.epoch_dev, peer.epoch_mul, peer.epoch_add));
+        } else if (peer.world > 1) mgpeer::store_all(peer, out + (size_t)h * head_dim + d, acc / L);
         else out[(size_t)h * head_dim + d] = acc / L;
     }
     mgpeer::peer_finish(peer);  // all-gather of the heads: the grid ends when every rank's heads are here

@@ -66,6 +66,19 @@ __device__ __forceinline__ void convert_chunk(const float (&v)[4], int chunk, ui
     // A non-finite activation poisons its sub-block: the scale becomes NaN, so every
     // row's sum becomes NaN as it does in the reference (w * NaN).
     const float sc = bad ? __uint_as_float(0x7FC00000u) : s;
+    if (peer != nullptr && peer->world > 1 && peer->stamp_slots != nullptr) {
+        // records all-gathered word by word, every word stamped with the exchange's epoch
+        const unsigned epoch = mgpeer::exchange_epoch(peer->epoch_dev, peer->epoch_mul, peer->epoch_add);
+        const long long w0 = plane - rec, r0 = r - rec;  // word offsets inside this rank's record slice
+        mgpeer::store_stamped_all(*peer, w0 + t, l2, epoch);
+        mgpeer::store_stamped_all(*peer, w0 + 8 + t, l1, epoch);
+        mgpeer::store_stamped_all(*peer, w0 + 16 + t, l0, epoch);
+        if (t == 0) {
+            mgpeer::store_stamped_all(*peer, r0 + 48 + (sub & 1), __float_as_uint(sc), epoch);
+            mgpeer::store_stamped_all(*peer, r0 + 50 + (sub & 1), __float_as_uint(sc * (float)sum), epoch);
+        }
+        return;
+    }
     if (peer != nullptr && peer->world > 1) {  // records all-gathered by the producing kernel
         mgpeer::store_all(*peer, plane + t, l2);
         mgpeer::store_all(*peer, plane + 8 + t, l1);
@@ -114,6 +127,12 @@ __device__ __forceinline__ void load_chunk(float (&v)[4], const float* x, int ch
     }
 }
 
+// Four consecutive activations out of a stamped vector: each slot is polled until it carries `epoch`.
+__device__ __forceinline__ void load_chunk_stamped(float (&v)[4], const mgpeer::StampIn& in, int chunk, unsigned epoch) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(mgpeer::ld_stamped(in, (long long)chunk * 4 + i, epoch));
+}
+
 // ---------------------------------------------------------------------------------------------
 // The streaming GEMV on limb records.
 // ---------------------------------------------------------------------------------------------
@@ -148,6 +167,8 @@ struct MatList {
     // exchange handshake (peer_sync.cuh): matvec and all-gather of the output slices in one kernel.
     // y (and addend) then point into this rank's arena.
     mgpeer::PeerSync peer;
+    // x (or the limb records) arrive as a stamped vector written by the peers: poll while staging.
+    mgpeer::StampIn xin;
 };
 template <int R>
 __device__ __forceinline__ int total_groups(const MatList& ml) {
@@ -293,7 +314,12 @@ __device__ __forceinline__ void stage_records(const MatList& ml, const void* src
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
             const int c = threadIdx.x + u * kGemvThreads;
-            if (c < n_chunks) load_chunk<COHERENT>(v[u], x, c, x_aligned);
+            if (c < n_chunks) {
+                if (ml.xin.slots != nullptr)
+                    load_chunk_stamped(v[u], ml.xin, c, mgpeer::exchange_epoch(ml.xin.epoch_dev, ml.xin.epoch_mul, ml.xin.epoch_add));
+                else
+                    load_chunk<COHERENT>(v[u], x, c, x_aligned);
+            }
         }
         if (ml.norm_w != nullptr) {
             // RMSNorm in front of the matvec (crates/modgrad-device/src/kfd/llm.rs:921-928, Plain)
@@ -335,8 +361,20 @@ __device__ __forceinline__ void stage_records(const MatList& ml, const void* src
     } else {
         const uint4* rec_g = static_cast<const uint4*>(src);
         const int n_vec = bpr * 4 * xlimbs::kRecordVec4;
-        for (int i = threadIdx.x; i < n_vec; i += kGemvThreads) cp_async16(&rec_s[i], &rec_g[i]);
-        cp_async_wait_all();
+        if (ml.xin.slots != nullptr) {  // stamped records: one slot per record word
+            const unsigned epoch = mgpeer::exchange_epoch(ml.xin.epoch_dev, ml.xin.epoch_mul, ml.xin.epoch_add);
+            for (int i = threadIdx.x; i < n_vec; i += kGemvThreads) {
+                uint4 w;
+                w.x = mgpeer::ld_stamped(ml.xin, (long long)i * 4 + 0, epoch);
+                w.y = mgpeer::ld_stamped(ml.xin, (long long)i * 4 + 1, epoch);
+                w.z = mgpeer::ld_stamped(ml.xin, (long long)i * 4 + 2, epoch);
+                w.w = mgpeer::ld_stamped(ml.xin, (long long)i * 4 + 3, epoch);
+                rec_s[i] = w;
+            }
+        } else {
+            for (int i = threadIdx.x; i < n_vec; i += kGemvThreads) cp_async16(&rec_s[i], &rec_g[i]);
+            cp_async_wait_all();
+        }
     }
     __syncthreads();
 }
@@ -396,7 +434,11 @@ __device__ __forceinline__ void gemv_body(const MatList& ml, const void* src, in
                 const float s = q4k::warp_sum(acc[r]);
                 if (lane == 0 && row0 + r < rows) {
                     const float v = add ? s + ld_f32<COHERENT>(add + row0 + r) : s;
-                    if (ml.peer.world > 1) mgpeer::store_all(ml.peer, y + row0 + r, v);
+                    if (ml.peer.world > 1 && ml.peer.stamp_slots != nullptr) {
+                        y[row0 + r] = v;
+                        mgpeer::store_stamped_all(ml.peer, row0 + r, __float_as_uint(v),
+                                                  mgpeer::exchange_epoch(ml.peer.epoch_dev, ml.peer.epoch_mul, ml.peer.epoch_add));
+                    } else if (ml.peer.world > 1) mgpeer::store_all(ml.peer, y + row0 + r, v);
                     else y[row0 + r] = v;
                 }
                 acc[r] = 0.0f;
@@ -607,7 +649,11 @@ __device__ __forceinline__ void gemv_ring_body(const MatList& ml, const void* sr
                 const float s = q4k::warp_sum(acc[r]);
                 if (lane == 0 && cons.row0 + r < rows) {
                     const float v = add ? s + add[cons.row0 + r] : s;
-                    if (ml.peer.world > 1) mgpeer::store_all(ml.peer, y + cons.row0 + r, v);
+                    if (ml.peer.world > 1 && ml.peer.stamp_slots != nullptr) {
+                        y[cons.row0 + r] = v;
+                        mgpeer::store_stamped_all(ml.peer, cons.row0 + r, __float_as_uint(v),
+                                                  mgpeer::exchange_epoch(ml.peer.epoch_dev, ml.peer.epoch_mul, ml.peer.epoch_add));
+                    } else if (ml.peer.world > 1) mgpeer::store_all(ml.peer, y + cons.row0 + r, v);
                     else y[cons.row0 + r] = v;
                 }
                 acc[r] = 0.0f;

@@ -58,7 +58,8 @@ struct mg_decoder {
     float *hidden = nullptr, *cur = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *gate = nullptr,
           *up = nullptr, *logits = nullptr;
     void *records = nullptr, *attn_scratch = nullptr, *argmax_scratch = nullptr;
-    int* state = nullptr;    // [0] position, [1] sequence length (position + 1), [2] step, [3] token
+    int* state = nullptr;    // [0] position, [1] sequence length (position + 1), [2] step, [3] token,
+                             // [4] tokens decoded since creation (never reset: the epoch of the stamped exchanges)
     int* history = nullptr;  // generated tokens
     int history_cap = 0;
     int n_splits = 1;
@@ -82,6 +83,8 @@ struct mg_decoder {
     // live in one arena that the other ranks' processes map with CUDA IPC.
     bool peer = false;   // gathers by peer stores (else NCCL)
     bool fused = false;  // ... done by the producing kernels themselves instead of a gather kernel
+    bool stamped = false;  // ... as stamped words (flag in data): no fence, no handshake, the consumer polls
+    unsigned long long *s_att = nullptr, *s_out = nullptr, *s_down = nullptr, *s_rec = nullptr;  // stamped vectors
     mgpeer::Exchange px;
     unsigned char* arena = nullptr;
     size_t arena_bytes = 0;
@@ -101,6 +104,7 @@ __global__ void advance_state_kernel(int* state) {
     state[0] += 1;
     state[1] += 1;
     state[2] += 1;
+    state[4] += 1;
 }
 
 int fail(mg_decoder* d, int code, const char* what) {
@@ -157,6 +161,35 @@ __global__ void local_pair_kernel(const float* logits, const int* local_tok, int
     mgpeer::peer_finish(peer);
 }
 
+// RMSNorm (crates/modgrad-device/src/kfd/llm.rs:921-928, Plain) of a stamped vector: the final norm
+// reads the hidden state straight out of the last down-projection's exchange.
+__global__ void __launch_bounds__(1024) rms_norm_stamped_kernel(const mgpeer::StampIn in, const float* weight, float* y,
+                                                                 int n, float eps) {
+    mg::pdl_prologue();
+    __shared__ float red[33];
+    const unsigned epoch = mgpeer::exchange_epoch(in.epoch_dev, in.epoch_mul, in.epoch_add);
+    float v[8], p = 0.0f;  // n <= 8192
+    for (int k = 0; k < 8; ++k) {
+        const int i = threadIdx.x + k * 1024;
+        v[k] = i < n ? __uint_as_float(mgpeer::ld_stamped(in, i, epoch)) : 0.0f;
+        p = fmaf(v[k], v[k], p);
+    }
+    for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(0xFFFFFFFFu, p, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = p;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = red[threadIdx.x];
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+        if (threadIdx.x == 0) red[32] = t;
+    }
+    __syncthreads();
+    const float inv = 1.0f / sqrtf(red[32] / (float)n + eps);
+    for (int k = 0; k < 8; ++k) {
+        const int i = threadIdx.x + k * 1024;
+        if (i < n) y[i] = v[k] * inv * weight[i];
+    }
+}
+
 int nccl_fail(mg_decoder* d, int code, const char* what) {
     d->last_error = std::string(what) + ": " + (mgnccl::api().GetErrorString ? mgnccl::api().GetErrorString(code) : "nccl");
     return (int)cudaErrorUnknown;
@@ -201,6 +234,29 @@ int gather_heads(mg_decoder* d) {
 
 int queue_token_impl(mg_decoder* d);
 
+// Stamped exchanges: the epoch of exchange `site` of layer `layer` in the current token is
+// tokens_decoded * (4 * n_layers + 4) + 4 * layer + site + 1: unique, increasing, never 0 (a zeroed
+// arena holds epoch 0), computed by producer and consumer from the same device counter.
+mgpeer::PeerSync stamp_out(mg_decoder* d, int site, unsigned long long* slots, long long index0, int layer) {
+    mgpeer::PeerSync ps = mgpeer::make_sync(d->px, site);
+    ps.stamp_slots = slots;
+    ps.epoch_dev = d->state + 4;
+    ps.epoch_mul = 4 * d->cfg.n_layers + 4;
+    ps.epoch_add = 4 * layer + site + 1;
+    ps.stamp_index0 = index0;
+    return ps;
+}
+mgpeer::StampIn stamp_in(mg_decoder* d, int site, const unsigned long long* slots, int layer) {
+    mgpeer::StampIn in;
+    in.slots = slots;
+    in.epoch_dev = d->state + 4;
+    in.epoch_mul = 4 * d->cfg.n_layers + 4;
+    in.epoch_add = 4 * layer + site + 1;
+    in.err = d->px.ctl + 2 * mgpeer::kMaxSites;
+    in.site = site;
+    return in;
+}
+
 // One token: embedding of state[3] -> logits -> arg-max into state[3].  Everything is queued
 // on d->stream; nothing synchronises.  The sharded engine chains NCCL collectives behind its
 // kernels, which may start as soon as their predecessor lets its successor launch: there the
@@ -235,6 +291,8 @@ int queue_token_impl(mg_decoder* d) {
             const uint8_t* w[3] = {L.wq, L.wk, L.wv};
             float* y[3] = {d->q, d->k, d->v};
             const int rows[3] = {q_loc, kv_loc, kv_loc};
+            // stamped: the hidden state is read out of the previous layer's down-projection exchange
+            if (d->stamped && l > 0) mgpeer::set_next_stamp_in(stamp_in(d, kSiteDown, d->s_down, l - 1));
             if ((e = mg_rmsnorm_matvec_q4k_multi_on_stream(3, w, d->hidden, L.attn_norm, c.rms_eps, nullptr, y, rows,
                                                            D / 256, s)))
                 return fail(d, e, "qkv");
@@ -244,7 +302,8 @@ int queue_token_impl(mg_decoder* d) {
             return fail(d, e, "rope");
         // this rank's heads land at their place in the full attention vector (and, fused, in
         // every peer's: the merge kernel ends with the exchange)
-        if (d->fused) mgpeer::set_next_peer_sync(mgpeer::make_sync(d->px, kSiteHeads));
+        if (d->stamped) mgpeer::set_next_peer_sync(stamp_out(d, kSiteHeads, d->s_att, (long long)d->h0 * hd, l));
+        else if (d->fused) mgpeer::set_next_peer_sync(mgpeer::make_sync(d->px, kSiteHeads));
         if ((e = mg_sdpa_decode_f16kv_on_stream(d->q, L.k_cache, L.v_cache, d->att_full + (size_t)d->h0 * hd, Hl, KVl,
                                                 hd, 0, seq_dev, scale, d->attn_scratch, d->n_splits, s)))
             return fail(d, e, "sdpa");
@@ -258,7 +317,10 @@ int queue_token_impl(mg_decoder* d) {
             float* y[1] = {in_place ? mine : d->tmp_full + (size_t)d->rank * d->d_loc};
             const float* add[1] = {in_place ? mine : nullptr};
             const int rows[1] = {d->d_loc};
-            if (d->fused) mgpeer::set_next_peer_sync(mgpeer::make_sync(d->px, kSiteOut));
+            if (d->stamped) {
+                mgpeer::set_next_stamp_in(stamp_in(d, kSiteHeads, d->s_att, l));
+                mgpeer::set_next_peer_sync(stamp_out(d, kSiteOut, d->s_out, (long long)d->rank * d->d_loc, l));
+            } else if (d->fused) mgpeer::set_next_peer_sync(mgpeer::make_sync(d->px, kSiteOut));
             if ((e = mg_matvec_q4k_multi_on_stream(1, w, d->att_full, 0, add, y, rows, q_dim / 256, s))) return fail(d, e, "o_proj");
         }
         if (sharded && !d->fused) {
@@ -269,13 +331,16 @@ int queue_token_impl(mg_decoder* d) {
             const uint8_t* w[2] = {L.wgate, L.wup};
             float* y[2] = {d->gate, d->up};
             const int rows[2] = {d->f_loc, d->f_loc};
+            if (d->stamped) mgpeer::set_next_stamp_in(stamp_in(d, kSiteOut, d->s_out, l));
             if ((e = mg_rmsnorm_matvec_q4k_multi_on_stream(2, w, d->hidden, L.ffn_norm, c.rms_eps, nullptr, y, rows,
                                                            D / 256, s)))
                 return fail(d, e, "gate_up");
         }
         {   // SwiGLU straight into limb records; a rank's slice is a whole number of records
             uint8_t* rec = static_cast<uint8_t*>(d->records) + mg_q4k_limb_record_bytes(d->f_loc) * d->rank;
-            if (d->fused) mgpeer::set_next_peer_sync(mgpeer::make_sync(d->px, kSiteRecords));
+            if (d->stamped)
+                mgpeer::set_next_peer_sync(stamp_out(d, kSiteRecords, d->s_rec, (long long)d->rank * (d->f_loc / 64) * 52, l));
+            else if (d->fused) mgpeer::set_next_peer_sync(mgpeer::make_sync(d->px, kSiteRecords));
             if ((e = mg_swiglu_limbs_on_stream(d->gate, d->up, nullptr, d->f_loc, rec, s))) return fail(d, e, "swiglu");
             if (!d->fused &&
                 (e = gather_equal(d, kSiteRecords, d->records, mg_q4k_limb_record_bytes(d->f_loc), mgnccl::kUint8, 1)))
@@ -288,7 +353,10 @@ int queue_token_impl(mg_decoder* d) {
             float* y[1] = {in_place ? mine : d->tmp_down + (size_t)d->rank * d->d_loc};
             const float* add[1] = {in_place ? mine : nullptr};
             const int rows[1] = {d->d_loc};
-            if (d->fused) mgpeer::set_next_peer_sync(mgpeer::make_sync(d->px, kSiteDown));
+            if (d->stamped) {
+                mgpeer::set_next_stamp_in(stamp_in(d, kSiteRecords, d->s_rec, l));
+                mgpeer::set_next_peer_sync(stamp_out(d, kSiteDown, d->s_down, (long long)d->rank * d->d_loc, l));
+            } else if (d->fused) mgpeer::set_next_peer_sync(mgpeer::make_sync(d->px, kSiteDown));
             if ((e = mg_matvec_q4k_multi_on_stream(1, w, d->records, 1, add, y, rows, F / 256, s))) return fail(d, e, "down");
         }
         if (sharded && !d->fused) {
@@ -296,7 +364,12 @@ int queue_token_impl(mg_decoder* d) {
             mg::launch_pdl(residual_add_kernel, dim3((D + 255) / 256), dim3(256), 0, d->stream, d->hidden, (const float*)d->tmp_down, D);
         }
     }
-    if ((e = launch_rms_norm_on_stream(d->hidden, d->out_norm, d->cur, 1, D, c.rms_eps, s))) return fail(d, e, "rms_norm");
+    if (d->stamped) {
+        if ((e = (int)mg::launch_pdl(rms_norm_stamped_kernel, dim3(1), dim3(1024), 0, d->stream,
+                                     stamp_in(d, kSiteDown, d->s_down, c.n_layers - 1), (const float*)d->out_norm, d->cur, D,
+                                     c.rms_eps)))
+            return fail(d, e, "rms_norm");
+    } else if ((e = launch_rms_norm_on_stream(d->hidden, d->out_norm, d->cur, 1, D, c.rms_eps, s))) return fail(d, e, "rms_norm");
     if ((e = mg_matvec_f16_on_stream(d->lm_head, d->cur, d->logits, d->v_loc, D, s))) return fail(d, e, "lm_head");
     if (!sharded) {
         if ((e = mg_argmax_on_stream(d->logits, c.vocab, tok_dev, d->argmax_scratch, d->history, step_dev, s)))
@@ -331,7 +404,9 @@ int setup_peer_exchange(mg_decoder* d) {
     const mgnccl::Api& n = mgnccl::api();
     const int world = d->world;
     // MODGRAD_DECODER_GATHER: "nccl" (NCCL collectives), "peer" (one peer-store gather kernel per
-    // collective), default "fused" (the producing kernels store to the peers themselves).
+    // collective), "fused" (the producing kernels store to the peers themselves and end with a flag
+    // handshake), default "stamped" (the same stores, every word carrying its epoch: no handshake,
+    // the consuming kernel polls the words it reads).
     const char* mode = getenv("MODGRAD_DECODER_GATHER");
     int want = !(mode && strcmp(mode, "nccl") == 0) && world <= mgpeer::kMaxRanks;
     struct Slot { cudaIpcMemHandle_t h; int ok; int pad[15]; };  // 128 bytes
@@ -373,6 +448,7 @@ int setup_peer_exchange(mg_decoder* d) {
         } else {
             d->peer = all;
             d->fused = all && !(mode && strcmp(mode, "peer") == 0);
+            d->stamped = d->fused && !(mode && strcmp(mode, "fused") == 0);
         }
     }
     if (d->peer) {
@@ -544,7 +620,9 @@ int mg_decoder_create_sharded(const mg_decoder_config* cfg, int rank, int world,
         auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
         const size_t o_att = mgpeer::kFlagBytes, o_out = o_att + up((size_t)q_dim * 4), o_down = o_out + up((size_t)D * 4),
                      o_rec = o_down + up((size_t)D * 4), o_pair = o_rec + up(mg_q4k_limb_record_bytes(F)),
-                     o_hid = o_pair + up((size_t)2 * mgpeer::kMaxRanks * 4), total = o_hid + up((size_t)D * 4);
+                     o_hid = o_pair + up((size_t)2 * mgpeer::kMaxRanks * 4), o_satt = o_hid + up((size_t)D * 4),
+                     o_sout = o_satt + up((size_t)q_dim * 8), o_sdown = o_sout + up((size_t)D * 8),
+                     o_srec = o_sdown + up((size_t)D * 8), total = o_srec + up((size_t)(F / 64) * 52 * 8);
         if ((rc = dev_alloc(d, &d->arena, total))) return bail(rc);
         if ((e = cudaMemset(d->arena, 0, total)) != cudaSuccess) return bail((int)e);
         d->arena_bytes = total;
@@ -554,6 +632,10 @@ int mg_decoder_create_sharded(const mg_decoder_config* cfg, int rank, int world,
         d->records = d->arena + o_rec;
         d->pair_buf = reinterpret_cast<float*>(d->arena + o_pair);
         d->hidden = reinterpret_cast<float*>(d->arena + o_hid);
+        d->s_att = reinterpret_cast<unsigned long long*>(d->arena + o_satt);
+        d->s_out = reinterpret_cast<unsigned long long*>(d->arena + o_sout);
+        d->s_down = reinterpret_cast<unsigned long long*>(d->arena + o_sdown);
+        d->s_rec = reinterpret_cast<unsigned long long*>(d->arena + o_srec);
     }
     if ((rc = dev_alloc(d, &d->gate, (size_t)d->f_loc))) return bail(rc);
     if ((rc = dev_alloc(d, &d->up, (size_t)d->f_loc))) return bail(rc);
@@ -568,7 +650,8 @@ int mg_decoder_create_sharded(const mg_decoder_config* cfg, int rank, int world,
     d->attn_scratch = tmp;
     if ((rc = dev_alloc(d, &tmp, (size_t)2 * 256 * 4 + 64))) return bail(rc);
     d->argmax_scratch = tmp;
-    if ((rc = dev_alloc(d, &d->state, (size_t)4))) return bail(rc);
+    if ((rc = dev_alloc(d, &d->state, (size_t)8))) return bail(rc);
+    if ((e = cudaMemset(d->state, 0, 8 * sizeof(int))) != cudaSuccess) return bail((int)e);
     d->history_cap = c.max_seq + 1;
     if ((rc = dev_alloc(d, &d->history, (size_t)d->history_cap))) return bail(rc);
     {   // inv_freq = base^(-2i/head_dim) as the CPU decoder evaluates it (llm.rs:958), rounded once
@@ -844,7 +927,7 @@ int mg_decoder_kernels_per_token(const mg_decoder* d) {
 // collective, 2 fused into the producing kernels; -1 for a single-GPU engine.
 int mg_decoder_gather_mode(const mg_decoder* d) {
     if (!d || d->world == 1) return -1;
-    return d->fused ? 2 : (d->peer ? 1 : 0);
+    return d->stamped ? 3 : (d->fused ? 2 : (d->peer ? 1 : 0));
 }
 
 }  // extern "C"

@@ -375,6 +375,9 @@ int speculation_for(cudaStream_t stream, const void* x, size_t x_bytes, const vo
 // lie inside this rank's arena, behind the flag block.
 bool peer_target_ok(const mgpeer::PeerSync& ps, const void* out, size_t bytes) {
     if (ps.world <= 1) return true;
+    if (ps.stamp_slots != nullptr)  // one 8-byte slot per 4-byte result word
+        return ps.epoch_dev != nullptr && ps.stamp_index0 >= 0 &&
+               mgpeer::in_arena(ps, ps.stamp_slots + ps.stamp_index0, bytes * 2);
     return mgpeer::in_arena(ps, out, bytes);
 }
 
@@ -489,6 +492,7 @@ bool fill_matlist(MatList& ml, int n_mats, const uint8_t* const* w, float* const
 extern "C" int mg_matvec_q4k_limbs_on_stream(const uint8_t* w_q4, const void* records, const float* bias,
                                              float* y, int out_dim, int blocks_per_row, void* stream) {
     const mgpeer::PeerSync peer = mgpeer::take_next_peer_sync();  // consumed on every path, errors included
+    (void)mgpeer::take_next_stamp_in();  // only the multi entry points read stamped input
     if (out_dim <= 0 || blocks_per_row <= 0) return (int)cudaErrorInvalidValue;
     if (w_q4 == nullptr || records == nullptr || y == nullptr) return (int)cudaErrorInvalidValue;
     if (!mg::aligned16(w_q4) || !mg::aligned16(records)) return (int)cudaErrorInvalidValue;
@@ -506,6 +510,7 @@ extern "C" int mg_matvec_q4k_limbs_on_stream(const uint8_t* w_q4, const void* re
 extern "C" int mg_matvec_q4k_bias_on_stream(const uint8_t* w_q4, const float* x, const float* bias,
                                             float* y, int out_dim, int blocks_per_row, void* stream) {
     const mgpeer::PeerSync peer = mgpeer::take_next_peer_sync();  // consumed on every path, errors included
+    (void)mgpeer::take_next_stamp_in();  // only the multi entry points read stamped input
     if (out_dim <= 0 || blocks_per_row <= 0) return (int)cudaErrorInvalidValue;
     if (w_q4 == nullptr || x == nullptr || y == nullptr) return (int)cudaErrorInvalidValue;
     if (!mg::aligned16(w_q4)) return (int)cudaErrorInvalidValue;
@@ -553,9 +558,11 @@ extern "C" int mg_matvec_q4k_multi_on_stream(int n_mats, const uint8_t* const* w
                                              int x_is_records, const float* const* addend, float* const* y,
                                              const int* out_dims, int blocks_per_row, void* stream) {
     const mgpeer::PeerSync peer = mgpeer::take_next_peer_sync();  // consumed on every path, errors included
+    const mgpeer::StampIn xin = mgpeer::take_next_stamp_in();
     if (blocks_per_row <= 0 || x == nullptr || !limbs_path_ok(blocks_per_row)) return (int)cudaErrorInvalidValue;
     MatList ml;
     if (!fill_matlist(ml, n_mats, w_q4, y, addend, out_dims)) return (int)cudaErrorInvalidValue;
+    ml.xin = xin;
     if (!peer_target_ok(peer, ml.y[0], (size_t)ml.rows[0] * sizeof(float))) return (int)cudaErrorInvalidValue;
     if (x_is_records) {
         if (!mg::aligned16(x)) return (int)cudaErrorInvalidValue;
@@ -573,9 +580,11 @@ extern "C" int mg_rmsnorm_matvec_q4k_multi_on_stream(int n_mats, const uint8_t* 
                                                      const float* const* addend, float* const* y,
                                                      const int* out_dims, int blocks_per_row, void* stream) {
     const mgpeer::PeerSync peer = mgpeer::take_next_peer_sync();  // consumed on every path, errors included
+    const mgpeer::StampIn xin = mgpeer::take_next_stamp_in();
     if (blocks_per_row <= 0 || blocks_per_row > kFusedConvertMaxBpr || !x || !norm_weight) return (int)cudaErrorInvalidValue;
     MatList ml;
     if (!fill_matlist(ml, n_mats, w_q4, y, addend, out_dims)) return (int)cudaErrorInvalidValue;
+    ml.xin = xin;
     if (!peer_target_ok(peer, ml.y[0], (size_t)ml.rows[0] * sizeof(float))) return (int)cudaErrorInvalidValue;
     ml.norm_w = norm_weight;
     ml.eps = eps;

@@ -58,12 +58,20 @@ PeerSync make_sync(const Exchange& ex, int site) {
     for (int r = 0; r < kSyncMaxRanks; ++r) ps.base[r] = r < ex.world ? ex.base[r] : nullptr;
     ps.ctl = ex.ctl;
     ps.arena_bytes = ex.bytes;
+    ps.stamp_slots = nullptr; ps.epoch_dev = nullptr; ps.epoch_mul = 0; ps.epoch_add = 0; ps.stamp_index0 = 0;
     ps.rank = ex.rank; ps.world = ex.world; ps.site = site;
     return ps;
 }
 
 namespace {
 thread_local PeerSync g_next = {};
+thread_local StampIn g_next_in = {};
+}
+void set_next_stamp_in(const StampIn& in) { g_next_in = in; }
+StampIn take_next_stamp_in() {
+    const StampIn in = g_next_in;
+    g_next_in = StampIn{};
+    return in;
 }
 void set_next_peer_sync(const PeerSync& ps) { g_next = ps; }
 PeerSync take_next_peer_sync() {

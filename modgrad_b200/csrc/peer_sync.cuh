@@ -17,6 +17,23 @@ struct PeerSync {
     unsigned* ctl;                       // local: [site] epoch, [kSyncMaxSites + site] ticket, [2*kSyncMaxSites] error
     unsigned long long arena_bytes;      // size of every rank's arena (all ranks lay theirs out identically)
     int rank, world, site;
+    // Stamped exchange (flag in data), used when stamp_slots != nullptr: every result word travels
+    // as ONE 64-bit word {epoch : value bits} stored into slot stamp_index0 + i of the vector at
+    // stamp_slots in every rank's arena (this rank's included); there is no fence, ticket or flag,
+    // and the producer does not wait.  epoch = *epoch_dev * epoch_mul + epoch_add.
+    unsigned long long* stamp_slots;
+    const int* epoch_dev;
+    int epoch_mul, epoch_add;
+    long long stamp_index0;
+};
+// The consumer's view of a stamped vector: slot i holds {epoch : bits}; a reader polls (bounded)
+// until the epoch it expects is there.  slots == nullptr: the input is an ordinary array.
+struct StampIn {
+    const unsigned long long* slots;
+    const int* epoch_dev;
+    int epoch_mul, epoch_add;
+    unsigned* err;  // the exchange's error word (ctl + 2 * kSyncMaxSites)
+    int site;
 };
 constexpr unsigned long long kSyncFlagBytes = 4096;  // head of every arena: the flags
 
@@ -58,11 +75,47 @@ __device__ __forceinline__ void store_all(const PeerSync& ps, T* local, T v) {
     for (int p = 0; p < ps.world; ++p)
         if (p != ps.rank) *peer_ptr(ps, p, local) = v;
 }
+// ---- stamped exchange ---------------------------------------------------------------------------
+__device__ __forceinline__ unsigned exchange_epoch(const int* epoch_dev, int mul, int add) {
+    return (unsigned)(*reinterpret_cast<const volatile int*>(epoch_dev)) * (unsigned)mul + (unsigned)add;
+}
+__device__ __forceinline__ void st_stamped(unsigned long long* p, unsigned bits, unsigned epoch) {
+    const unsigned long long v = ((unsigned long long)epoch << 32) | bits;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// Word `bits` of element `index` of this rank's slice goes to every rank (this one included).
+__device__ __forceinline__ void store_stamped_all(const PeerSync& ps, long long index, unsigned bits, unsigned epoch) {
+    unsigned long long* local = ps.stamp_slots + ps.stamp_index0 + index;
+    for (int p = 0; p < ps.world; ++p) st_stamped(p == ps.rank ? local : peer_ptr(ps, p, local), bits, epoch);
+}
+__device__ __forceinline__ unsigned long long ld_stamped_raw(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+// Polls slot p until it carries `epoch` (bounded: a slot that never arrives sets the error word to
+// 1 + site, after which every later poll of the exchange gives up at once); returns the value bits.
+__device__ __forceinline__ unsigned ld_stamped(const StampIn& in, long long index, unsigned epoch) {
+    const unsigned long long* p = in.slots + index;
+    unsigned spins = 0;
+    for (;;) {
+        const unsigned long long v = ld_stamped_raw(p);
+        if ((unsigned)(v >> 32) == epoch) return (unsigned)v;
+        if ((++spins & 1023u) == 0) {
+            if (*reinterpret_cast<volatile unsigned*>(in.err) != 0u) return 0u;
+            if (spins > kSyncSpinLimit) {
+                atomicCAS(in.err, 0u, (unsigned)in.site + 1u);
+                return 0u;
+            }
+        }
+    }
+}
+
 // Called by ALL threads of EVERY CTA of the grid after their last peer store.  The last CTA to
 // arrive publishes this rank's epoch on every peer and waits (bounded) for the peers' epochs; the
 // grid therefore completes only when the whole gathered buffer is in local memory.
 __device__ __forceinline__ void peer_finish(const PeerSync& ps) {
-    if (ps.world <= 1) return;
+    if (ps.world <= 1 || ps.stamp_slots != nullptr) return;  // stamped results need no handshake
     __syncthreads();  // every thread of the CTA has issued its peer stores
     if (threadIdx.x != 0) return;
     __threadfence_system();  // ... and they are performed (cumulatively) before the ticket below
@@ -101,5 +154,9 @@ __device__ __forceinline__ void peer_finish(const PeerSync& ps) {
 // (reset to "none") by that launch.
 void set_next_peer_sync(const PeerSync& ps);
 PeerSync take_next_peer_sync();
+// The stamped vector the NEXT launch of a kernel that supports it (the Q4_K matvecs with f32 x or
+// limb records) reads its input from; same rules.
+void set_next_stamp_in(const StampIn& in);
+StampIn take_next_stamp_in();
 
 }  // namespace mgpeer

@@ -252,5 +252,6 @@ class Q4KDecoder:
 
     def gather_mode(self) -> str:
         """How a sharded engine all-gathers its slices: "nccl", "peer" (one peer-store gather
-        kernel per collective) or "fused" (inside the producing kernels); "none" on one GPU."""
-        return {-1: "none", 0: "nccl", 1: "peer", 2: "fused"}[int(self._lib.mg_decoder_gather_mode(self._h))]
+        kernel per collective), "fused" (inside the producing kernels, flag handshake at their end) or
+        "stamped" (inside the producing kernels, every word carrying its epoch); "none" on one GPU."""
+        return {-1: "none", 0: "nccl", 1: "peer", 2: "fused", 3: "stamped"}[int(self._lib.mg_decoder_gather_mode(self._h))]

@@ -48,7 +48,7 @@ def main():
         assert not bad, bad
     modes = [None] * world
     dist.all_gather_object(modes, d.gather_mode())
-    assert all(m == os.environ.get("MODGRAD_DECODER_GATHER", "fused") for m in modes), modes
+    assert all(m == os.environ.get("MODGRAD_DECODER_GATHER", "stamped") for m in modes), modes
     d.set_position(0)
     toks, ms = d.generate(3, 8)
     gathered = [None] * world

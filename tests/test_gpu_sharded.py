@@ -19,7 +19,8 @@ def gpu_count(cuda) -> int:
     return n.value if cuda.mg_get_device_count(C.byref(n)) == 0 else 0
 
 
-@pytest.mark.parametrize("world,mode", [(2, "fused"), (2, "peer"), (2, "nccl"), (4, "fused")])
+@pytest.mark.parametrize("world,mode", [(2, "stamped"), (2, "fused"), (2, "peer"), (2, "nccl"), (4, "stamped"), (4, "fused"),
+                                        (8, "stamped"), (8, "nccl")])
 def test_sharded_decoder_matches_oracle(cuda, world, mode):
     if gpu_count(cuda) < world:
         pytest.skip(f"needs {world} GPUs")
