@@ -290,6 +290,9 @@ int mg_decoder_kernels_per_token(const mg_decoder* d);
  * 2 = the all-gathers are fused into the producing kernels (default when every rank can map its
  * peers; MODGRAD_DECODER_GATHER=nccl|peer|fused overrides); -1 on a single GPU. */
 int mg_decoder_gather_mode(const mg_decoder* d);
+/* Polls a bounded wait of the engine's peer exchanges makes before it gives up and the token fails
+ * with cudaErrorLaunchTimeout (default 1 << 22, seconds); call before the first token. */
+int mg_decoder_set_exchange_spin_limit(mg_decoder* d, unsigned polls);
 
 /* The single device allocation that holds every weight tensor of the engine (the reference packs
  * its quantised tensors the same way, crates/modgrad-gemma/src/rocm_gemma.rs:206-224) and the
@@ -391,6 +394,7 @@ int mg_peer_fuse_next(mg_peer_exchange* x, int site);
 int mg_peer_gather_on_stream(mg_peer_exchange* x, int site, size_t offset, size_t my_off, size_t my_bytes,
                              void* stream);
 int mg_peer_exchange_status(mg_peer_exchange* x);
+int mg_peer_exchange_set_spin_limit(mg_peer_exchange* x, unsigned polls);
 void mg_peer_exchange_destroy(mg_peer_exchange* x);
 
 /* ---- the operator/plugin tier above the launchers ------------------------------------------

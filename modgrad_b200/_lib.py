@@ -56,6 +56,8 @@ SIGNATURES = {
     "mg_peer_fuse_next": (ci, [vp, ci]),
     "mg_peer_gather_on_stream": (ci, [vp, ci, sz, sz, sz, vp]),
     "mg_peer_exchange_status": (ci, [vp]),
+    "mg_peer_exchange_set_spin_limit": (ci, [vp, C.c_uint]),
+    "mg_decoder_set_exchange_spin_limit": (ci, [vp, C.c_uint]),
     "mg_peer_exchange_destroy": (None, [vp]),
     "mg_q4k_x_to_limbs_on_stream": (ci, [vp, ci, vp, vp]),
     "mg_matvec_q4k_limbs_on_stream": (ci, [vp, vp, vp, vp, ci, ci, vp]),

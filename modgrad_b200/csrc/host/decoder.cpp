@@ -254,6 +254,7 @@ mgpeer::StampIn stamp_in(mg_decoder* d, int site, const unsigned long long* slot
     in.epoch_add = 4 * layer + site + 1;
     in.err = d->px.ctl + 2 * mgpeer::kMaxSites;
     in.site = site;
+    in.spin_limit = d->px.spin_limit;
     return in;
 }
 
@@ -922,6 +923,13 @@ int mg_decoder_kernels_per_token(const mg_decoder* d) {
     int n = 1 + d->cfg.n_layers * (d->fused ? 8 : 10) + 7;
     if (d->peer && !d->fused) n += 4 * d->cfg.n_layers + 1;
     return n;
+}
+// Polls a bounded wait of the engine's peer exchanges makes before it gives up (default 1 << 22).
+// Takes effect for graphs captured afterwards: call it before the first token.
+int mg_decoder_set_exchange_spin_limit(mg_decoder* d, unsigned polls) {
+    if (!d || polls == 0 || d->graph_exec) return (int)cudaErrorInvalidValue;
+    d->px.spin_limit = polls;
+    return 0;
 }
 // How the sharded engine gathers: 0 NCCL collectives, 1 one peer-store gather kernel per
 // collective, 2 fused into the producing kernels; -1 for a single-GPU engine.

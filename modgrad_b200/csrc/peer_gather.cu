@@ -60,6 +60,7 @@ PeerSync make_sync(const Exchange& ex, int site) {
     ps.arena_bytes = ex.bytes;
     ps.stamp_slots = nullptr; ps.epoch_dev = nullptr; ps.epoch_mul = 0; ps.epoch_add = 0; ps.stamp_index0 = 0;
     ps.rank = ex.rank; ps.world = ex.world; ps.site = site;
+    ps.spin_limit = ex.spin_limit;
     return ps;
 }
 
@@ -157,6 +158,14 @@ int mg_peer_gather_on_stream(mg_peer_exchange* x, int site, size_t offset, size_
                              void* stream) {
     if (!x) return (int)cudaErrorInvalidValue;
     return (int)mgpeer::launch_gather(x->ex, site, offset, my_off, my_bytes, (cudaStream_t)stream);
+}
+// Polls a bounded wait of this exchange makes before it gives up and sets the error word (default
+// 1 << 22, a few seconds; a test that lets a wait run out on purpose lowers it).  Applies to
+// launches armed afterwards.
+int mg_peer_exchange_set_spin_limit(mg_peer_exchange* x, unsigned polls) {
+    if (!x || polls == 0) return (int)cudaErrorInvalidValue;
+    x->ex.spin_limit = polls;
+    return 0;
 }
 // 0, or 1 + the site whose bounded wait ran out since creation; negative = -(CUDA error).
 int mg_peer_exchange_status(mg_peer_exchange* x) {

@@ -30,6 +30,7 @@ struct Exchange {
     unsigned char* base[kMaxRanks] = {};  // base[r]: rank r's arena as mapped in this process
     unsigned* ctl = nullptr;              // local control words: epochs, tickets, error (see .cu)
     size_t bytes = 0;                     // size of the arena (the same on every rank)
+    unsigned spin_limit = kSyncSpinLimit; // polls before a bounded wait gives up
 };
 constexpr size_t kCtlWords = 2 * kMaxSites + 1;
 static_assert(kMaxRanks == kSyncMaxRanks && kMaxSites == kSyncMaxSites && kFlagBytes == kSyncFlagBytes, "one layout");

@@ -17,6 +17,7 @@ struct PeerSync {
     unsigned* ctl;                       // local: [site] epoch, [kSyncMaxSites + site] ticket, [2*kSyncMaxSites] error
     unsigned long long arena_bytes;      // size of every rank's arena (all ranks lay theirs out identically)
     int rank, world, site;
+    unsigned spin_limit;  // polls of a flag before a wait gives up (kSyncSpinLimit unless the host lowered it)
     // Stamped exchange (flag in data), used when stamp_slots != nullptr: every result word travels
     // as ONE 64-bit word {epoch : value bits} stored into slot stamp_index0 + i of the vector at
     // stamp_slots in every rank's arena (this rank's included); there is no fence, ticket or flag,
@@ -34,6 +35,7 @@ struct StampIn {
     int epoch_mul, epoch_add;
     unsigned* err;  // the exchange's error word (ctl + 2 * kSyncMaxSites)
     int site;
+    unsigned spin_limit;
 };
 constexpr unsigned long long kSyncFlagBytes = 4096;  // head of every arena: the flags
 
@@ -103,7 +105,7 @@ __device__ __forceinline__ unsigned ld_stamped(const StampIn& in, long long inde
         if ((unsigned)(v >> 32) == epoch) return (unsigned)v;
         if ((++spins & 1023u) == 0) {
             if (*reinterpret_cast<volatile unsigned*>(in.err) != 0u) return 0u;
-            if (spins > kSyncSpinLimit) {
+            if (spins > in.spin_limit) {
                 atomicCAS(in.err, 0u, (unsigned)in.site + 1u);
                 return 0u;
             }
@@ -140,7 +142,7 @@ __device__ __forceinline__ void peer_finish(const PeerSync& ps) {
         const unsigned* f = flag_of(ps.base[ps.rank], ps.site, p);
         unsigned spins = 0;
         while ((int)(ld_acquire_sys(f) - epoch) < 0) {
-            if (++spins > kSyncSpinLimit) {  // a peer never arrived: report it, keep the context usable
+            if (++spins > ps.spin_limit) {  // a peer never arrived: report it, keep the context usable
                 atomicCAS(ps.ctl + 2 * kSyncMaxSites, 0u, (unsigned)ps.site + 1u);
                 return;
             }

@@ -247,6 +247,10 @@ class Q4KDecoder:
         self._check(self._lib.mg_decoder_generate(self._h, int(first_token), n_tokens, _p(out), C.byref(ms)), "generate")
         return out, float(ms.value)
 
+    def set_exchange_spin_limit(self, polls: int):
+        """Polls a bounded wait of the peer exchanges makes before the token fails (before the first token)."""
+        self._check(self._lib.mg_decoder_set_exchange_spin_limit(self._h, int(polls)), "set_exchange_spin_limit")
+
     def kernels_per_token(self) -> int:
         return int(self._lib.mg_decoder_kernels_per_token(self._h))
 

@@ -31,3 +31,20 @@ def test_sharded_decoder_matches_oracle(cuda, world, mode):
                        env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
     assert "SHARDED_OK" in r.stdout and "PEER_MATVEC_OK" in r.stdout, r.stdout[-1500:]
+
+
+@pytest.mark.parametrize("mode", ["stamped", "fused"])
+def test_bounded_wait_runs_out_when_a_peer_does_not_launch(cuda, mode):
+    """A peer that skips a step between launches: the waiting rank's bounded wait expires, the token
+    fails with a time-out that names the exchange, later tokens fail at once, the context stays
+    usable.  No GPU is faulted or hung (NVLS off, plain peer stores)."""
+    if gpu_count(cuda) < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MODGRAD_DECODER_GATHER=mode)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29650", str(ROOT / "tests" / "timeout_worker.py")],
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
+    line = [l for l in r.stdout.splitlines() if l.startswith("TIMEOUT_RESULT")]
+    assert line, r.stdout[-1500:]
+    assert "timeout:" in line[0] and "did not arrive" in line[0] and "second failed" in line[0], line[0]
