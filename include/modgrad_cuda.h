@@ -225,6 +225,9 @@ int launch_sdpa_decode_flash(const float* q, const float* k_cache, const float* 
 int launch_sdpa_decode_on_stream(const float* q, const float* k_cache, const float* v_cache, float* out,
                                  int n_heads, int n_kv_heads, int head_dim, int seq_len, int kv_dim, float scale,
                                  int win_start, void* stream);
+int launch_sdpa_decode_flash_on_stream(const float* q, const float* k_cache, const float* v_cache, float* out,
+                                       int n_heads, int n_kv_heads, int head_dim, int seq_len, int kv_dim, float scale,
+                                       int win_start, void* stream);
 
 /* The same attention over a HALF cache, split over the sequence (the 7B-class decoder keeps
  * K/V in half precision; the reference keeps f32, rocm_gemma.rs:256-261).  `scratch` holds the

@@ -86,6 +86,7 @@ SIGNATURES = {
     "launch_sdpa_decode": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci]),
     "launch_sdpa_decode_flash": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci]),
     "launch_sdpa_decode_on_stream": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, vp]),
+    "launch_sdpa_decode_flash_on_stream": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, vp]),
     "mg_sdpa_f16kv_scratch_bytes": (sz, [ci, ci, ci]),
     "mg_sdpa_decode_f16kv_on_stream": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, vp, cf, vp, ci, vp]),
     "mg_rope_kv_append_f16_on_stream": (ci, [vp, vp, vp, vp, vp, ci, vp, ci, ci, ci, cf, vp, vp]),

@@ -330,6 +330,12 @@ int launch_sdpa_decode_flash(const float* q, const float* k_cache, const float* 
     return launch_sdpa_decode_on_stream(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim, seq_len,
                                         kv_dim, scale, win_start, nullptr);
 }
+int launch_sdpa_decode_flash_on_stream(const float* q, const float* k_cache, const float* v_cache, float* out,
+                                       int n_heads, int n_kv_heads, int head_dim, int seq_len, int kv_dim, float scale,
+                                       int win_start, void* stream) {
+    return launch_sdpa_decode_on_stream(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim, seq_len,
+                                        kv_dim, scale, win_start, stream);
+}
 
 size_t mg_sdpa_f16kv_scratch_bytes(int n_heads, int head_dim, int n_splits) {
     if (n_heads <= 0 || head_dim <= 0 || n_splits <= 0) return 0;

@@ -467,21 +467,6 @@ __device__ __forceinline__ void gemv_body(const MatList& ml, const void* src, in
 // before the kernel waits for its predecessor, so the stream is already running while x is
 // converted.
 // ---------------------------------------------------------------------------------------------
-// Optional timeline instrumentation for bring-up builds (compiled out of the library).
-#ifdef GEMV_TRACE
-static __device__ unsigned long long* g_gemv_trace = nullptr;  // [cta][warp][32] timestamps
-#define GEMV_TRACE_MARK(slot)                                                                          \
-    do {                                                                                               \
-        if (g_gemv_trace && (threadIdx.x & 31) == 0 && (slot) < 32) {                                  \
-            unsigned long long t_;                                                                     \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                     \
-            g_gemv_trace[((size_t)blockIdx.x * kGemvWarps + (threadIdx.x >> 5)) * 32 + (slot)] = t_;   \
-        }                                                                                              \
-    } while (0)
-#else
-#define GEMV_TRACE_MARK(slot) do { } while (0)
-#endif
-
 constexpr int kRingMaxDepth = 4;
 constexpr uint32_t kRingSpinLimit = 1u << 22;  // polls of one stage before the warp gives up
 
@@ -557,7 +542,6 @@ __device__ __forceinline__ void gemv_ring_body(const MatList& ml, const void* sr
     const int total = my_groups * n_win;
     const uint32_t sel_sc = 0x4440u + (uint32_t)((g & 1) * 2);
 
-    GEMV_TRACE_MARK(0);
     if (!ml.hold_trigger) griddep_launch_dependents();
 
     // Fills stage `st` with the unit at cursor `c`; all lanes call it, lanes 0..R-1 copy.
@@ -603,11 +587,8 @@ __device__ __forceinline__ void gemv_ring_body(const MatList& ml, const void* sr
         advance(prod);
     }
 
-    GEMV_TRACE_MARK(1);
     griddep_wait();  // x / the records may be produced by the kernel launched just before this one
-    GEMV_TRACE_MARK(2);
     stage_records<FROM_X, false>(ml, src, x_aligned, bpr, rec_s);
-    GEMV_TRACE_MARK(3);
 
     float acc[R];
 #pragma unroll
@@ -628,7 +609,6 @@ __device__ __forceinline__ void gemv_ring_body(const MatList& ml, const void* sr
             if (lane == 0) atomicAdd(timeouts, 1u);
             break;
         }
-        GEMV_TRACE_MARK(4 + 2 * t);
         const bool active = cons.win * 8 + bl < bpr;
         Window<R> wd;
         if (active) load_window_smem<R>(wd, ring + st * stage_bytes, row_stride, bl, g);
@@ -664,7 +644,6 @@ __device__ __forceinline__ void gemv_ring_body(const MatList& ml, const void* sr
             st = 0;
             parity ^= 1u;
         }
-        GEMV_TRACE_MARK(5 + 2 * t);
     }
     mgpeer::peer_finish(ml.peer);
 }

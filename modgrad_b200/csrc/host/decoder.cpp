@@ -29,7 +29,6 @@
 #include <string>
 #include <vector>
 
-#include "../decode_persistent.hpp"
 #include "../launch_common.cuh"
 #include "../peer_gather.hpp"
 #include "modgrad_cuda.h"
@@ -89,12 +88,6 @@ struct mg_decoder {
     unsigned char* arena = nullptr;
     size_t arena_bytes = 0;
     std::vector<void*> ipc_opened;
-    // ---- persistent per-token kernel (single GPU) -----------------------------------------------
-    bool persistent = false;
-    mgdec::PArgs pargs{};
-    mgdec::PLayer* players = nullptr;
-    unsigned* barrier = nullptr;
-    int* error_word = nullptr;
 };
 
 namespace {
@@ -390,14 +383,6 @@ int queue_token_impl(mg_decoder* d) {
     return 0;
 }
 
-// One token as ONE cooperative launch of the persistent kernel.
-int queue_token_persistent(mg_decoder* d) {
-    cudaError_t e = cudaMemsetAsync(d->barrier, 0, sizeof(unsigned), d->stream);
-    if (e != cudaSuccess) return fail(d, (int)e, "barrier reset");
-    e = mgdec::launch_decode_token(d->pargs, d->stream);
-    if (e != cudaSuccess) return fail(d, (int)e, "persistent decode launch");
-    return 0;
-}
 // Maps every rank's arena into this process (CUDA IPC handles exchanged with an NCCL all-gather)
 // so that the per-layer gathers can be direct peer stores.  Falls back to NCCL gathers — on all
 // ranks together — when any rank cannot map its peers, or when MODGRAD_DECODER_GATHER=nccl.
@@ -470,20 +455,7 @@ int check_peer_error(mg_decoder* d) {
     return 0;
 }
 
-int check_persistent_error(mg_decoder* d) {
-    int w = 0;
-    cudaError_t e = cudaMemcpy(&w, d->error_word, sizeof(int), cudaMemcpyDeviceToHost);
-    if (e != cudaSuccess) return fail(d, (int)e, "error word");
-    if (w) {
-        cudaMemset(d->error_word, 0, sizeof(int));
-        d->last_error = "persistent decode kernel: a bounded grid-barrier wait expired";
-        return (int)cudaErrorLaunchTimeout;
-    }
-    return 0;
-}
-
 int ensure_graph(mg_decoder* d) {
-    if (d->persistent) return 0;
     if (d->graph_exec) return 0;
     // A first pass outside capture sets every kernel attribute (function attributes cannot be
     // changed while capturing); it is undone by restoring the device state afterwards.
@@ -664,43 +636,6 @@ int mg_decoder_create_sharded(const mg_decoder_config* cfg, int rank, int world,
     int init[4] = {0, 1, 0, 0};
     if ((e = cudaMemcpy(d->state, init, sizeof init, cudaMemcpyHostToDevice)) != cudaSuccess) return bail((int)e);
     if (world > 1 && (rc = setup_peer_exchange(d))) return bail(rc);
-    // MODGRAD_DECODER_PERSISTENT=1 (single GPU): one persistent cooperative kernel per token
-    // instead of the graph of separate kernels.  Off by default: on B200 a software grid barrier
-    // costs about as much as a kernel boundary (three L2 round trips, ~4 us), so the persistent
-    // kernel measured 3.1 ms/token against 2.25 ms/token for the graph.
-    const char* want_persistent = getenv("MODGRAD_DECODER_PERSISTENT");
-    if (world == 1 && want_persistent && want_persistent[0] == '1' &&
-        mgdec::persistent_supported(c.n_heads, c.n_kv_heads, hd, D, F) && sms >= c.n_kv_heads) {
-        std::vector<mgdec::PLayer> pl(c.n_layers);
-        for (int l = 0; l < c.n_layers; ++l) {
-            const Layer& L = d->layers[l];
-            pl[l] = mgdec::PLayer{L.wq, L.wk, L.wv, L.wo, L.wgate, L.wup, L.wdown, L.attn_norm, L.ffn_norm, L.k_cache, L.v_cache};
-        }
-        uint8_t* raw = nullptr;
-        if ((rc = dev_alloc(d, &raw, pl.size() * sizeof(mgdec::PLayer)))) return bail(rc);
-        d->players = reinterpret_cast<mgdec::PLayer*>(raw);
-        if ((e = cudaMemcpy(d->players, pl.data(), pl.size() * sizeof(mgdec::PLayer), cudaMemcpyHostToDevice)) != cudaSuccess)
-            return bail((int)e);
-        if ((rc = dev_alloc(d, &d->barrier, (size_t)1))) return bail(rc);
-        if ((rc = dev_alloc(d, &d->error_word, (size_t)1))) return bail(rc);
-        if ((e = cudaMemset(d->error_word, 0, sizeof(int))) != cudaSuccess) return bail((int)e);
-        mgdec::PArgs& a = d->pargs;
-        a.layers = d->players; a.n_layers = c.n_layers; a.d_model = D; a.n_heads = c.n_heads;
-        a.n_kv_heads = c.n_kv_heads; a.head_dim = hd; a.d_ff = F; a.vocab = c.vocab; a.eps = c.rms_eps;
-        a.embed = d->embed; a.lm_head = d->lm_head; a.out_norm = d->out_norm; a.rope_freq = d->rope_freq;
-        a.hidden = d->hidden; a.q = d->q; a.k = d->k; a.v = d->v; a.att = d->att_full; a.gate = d->gate; a.up = d->up;
-        a.logits = d->logits; a.records = d->records; a.partial = static_cast<float*>(d->attn_scratch);
-        a.amax_val = static_cast<float*>(d->argmax_scratch);
-        a.amax_idx = reinterpret_cast<int*>(static_cast<char*>(d->argmax_scratch) + 1024);
-        a.state = d->state; a.history = d->history; a.barrier = d->barrier; a.error = d->error_word;
-        a.timing = nullptr;
-        if (getenv("MODGRAD_DECODER_TIMING")) {
-            uint8_t* t = nullptr;
-            if ((rc = dev_alloc(d, &t, (size_t)8 * (c.n_layers * 7 + 8)))) return bail(rc);
-            a.timing = reinterpret_cast<unsigned long long*>(t);
-        }
-        d->persistent = true;
-    }
     *out = d;
     return 0;
 }
@@ -794,24 +729,9 @@ int mg_decoder_forward_token(mg_decoder* d, int token, float* logits_host, int* 
     if (rc) return rc;
     cudaError_t e = cudaMemcpyAsync(d->state + 3, &token, sizeof(int), cudaMemcpyHostToDevice, d->stream);
     if (e != cudaSuccess) return fail(d, (int)e, "token upload");
-    if (d->persistent) {
-        if ((rc = queue_token_persistent(d))) return rc;
-    } else if ((e = cudaGraphLaunch(d->graph_exec, d->stream)) != cudaSuccess) {
-        return fail(d, (int)e, "graph launch");
-    }
+    if ((e = cudaGraphLaunch(d->graph_exec, d->stream)) != cudaSuccess) return fail(d, (int)e, "graph launch");
     if ((e = cudaStreamSynchronize(d->stream)) != cudaSuccess) return fail(d, (int)e, "sync");
-    if (d->persistent && (rc = check_persistent_error(d))) return rc;
     if ((rc = check_peer_error(d))) return rc;
-    if (d->persistent && d->pargs.timing) {  // bring-up aid: per-phase time of a middle layer
-        const int n = d->cfg.n_layers * 7 + 4;
-        std::vector<unsigned long long> t((size_t)n + 1);
-        cudaMemcpy(t.data(), d->pargs.timing, t.size() * 8, cudaMemcpyDeviceToHost);
-        const int l = d->cfg.n_layers / 2, base = 1 + l * 7;
-        const char* names[7] = {"qkv", "attention", "merge", "o", "gate_up", "swiglu", "down"};
-        fprintf(stderr, "[decode phases, layer %d]", l);
-        for (int i = 0; i < 7; ++i) fprintf(stderr, " %s=%.2fus", names[i], (double)(t[base + i + 1] - t[base + i]) * 1e-3);
-        fprintf(stderr, " | lm_head=%.2fus total=%.2fus\n", (double)(t[n - 1] - t[n - 2]) * 1e-3, (double)(t[n] - t[1]) * 1e-3);
-    }
     d->pos_host += 1;
     if (logits_host) {
         e = cudaMemcpy(logits_host, d->logits, (size_t)d->v_loc * 4, cudaMemcpyDeviceToHost);  // this rank's slice
@@ -844,11 +764,7 @@ int mg_decoder_generate(mg_decoder* d, int first_token, int n_tokens, int* out_t
     cudaEventCreate(&b);
     cudaEventRecord(a, d->stream);
     for (int i = 0; i < n_tokens; ++i) {
-        if (d->persistent) {
-            if ((rc = queue_token_persistent(d))) { e = cudaErrorUnknown; break; }
-        } else if ((e = cudaGraphLaunch(d->graph_exec, d->stream)) != cudaSuccess) {
-            break;
-        }
+        if ((e = cudaGraphLaunch(d->graph_exec, d->stream)) != cudaSuccess) break;
     }
     cudaEventRecord(b, d->stream);
     cudaError_t es = cudaStreamSynchronize(d->stream);
@@ -858,7 +774,6 @@ int mg_decoder_generate(mg_decoder* d, int first_token, int n_tokens, int* out_t
     cudaEventDestroy(b);
     if (e != cudaSuccess) return fail(d, (int)e, "graph launch");
     if (es != cudaSuccess) return fail(d, (int)es, "sync");
-    if (d->persistent && (rc = check_persistent_error(d))) return rc;
     if ((rc = check_peer_error(d))) return rc;
     d->pos_host += n_tokens;
     if (device_ms) *device_ms = ms;
@@ -916,7 +831,6 @@ void* mg_decoder_weight_ptr(mg_decoder* d, int layer, int which) {
 }
 int mg_decoder_kernels_per_token(const mg_decoder* d) {
     if (!d) return 0;
-    if (d->persistent) return 1;
     if (d->world == 1) return 1 + d->cfg.n_layers * 8 + 5;
     // sharded: + the pair kernels at the end; + two residual adds per layer unless the matvecs
     // add in place (fused); + one gather kernel per collective in the peer-kernel mode

@@ -283,18 +283,15 @@ cudaError_t launch_ring(const MatList& ml, const void* src, int bpr, int depth, 
 // Ring kernel when at least two stages per warp fit, else the register-load kernel.
 template <int R, int FROM_X>
 cudaError_t launch_gemv(const MatList& ml, const void* src, int bpr, int sms, cudaStream_t stream) {
-    static const bool no_ring = [] {
-        const char* e = getenv("MODGRAD_Q4K_GEMV_NO_RING");
-        return e && e[0] == '1';
-    }();
     const int depth = ring_depth(bpr, R);
-    if (depth >= 2 && !no_ring) return launch_ring<R, FROM_X>(ml, src, bpr, depth, sms, stream);
+    if (depth >= 2) return launch_ring<R, FROM_X>(ml, src, bpr, depth, sms, stream);
     return launch_dp4a<R, FROM_X>(ml, src, bpr, sms, stream);
 }
 
-// Per (device, stream) scratch for the limb records of long activation vectors (two halves
-// used alternately: the conversion of call N+1 may start while the GEMV of call N still
-// reads its records, because both kernels allow early launch of their successor).
+// Per (device, stream) scratch for the limb records of long activation vectors.  Every kernel of
+// this library waits for its predecessor in the stream to COMPLETE before it writes (or reads)
+// anything the predecessor touches, so one table per stream would do; two halves used alternately
+// keep the conversion of call N+1 off the lines the GEMV of call N has just read.
 struct Workspace {
     void* ptr = nullptr;
     size_t bytes = 0;  // of one half
@@ -628,20 +625,21 @@ extern "C" int launch_matvec_q4k_noalloc_on_stream(const uint8_t* w_q4, const fl
         return (int)cudaErrorInvalidValue;
     }
     // In host code the array's name is only a stand-in; the kernels need its device address.
-    static void* dev_ptr[64] = {};
+    // (host threads may race to be first on a device: the slot is atomic and every racer stores the same address)
+    static std::atomic<void*> dev_ptr[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
-    if (dev_ptr[dev] == nullptr) {
-        void* p = nullptr;
-        e = cudaGetSymbolAddress(&p, g_noalloc_records);
+    void* records = dev_ptr[dev].load(std::memory_order_acquire);
+    if (records == nullptr) {
+        e = cudaGetSymbolAddress(&records, g_noalloc_records);
         if (e != cudaSuccess) return (int)e;
-        dev_ptr[dev] = p;
+        dev_ptr[dev].store(records, std::memory_order_release);
     }
-    const int rc = mg_q4k_x_to_limbs_on_stream(x, blocks_per_row * 256, dev_ptr[dev], stream);
+    const int rc = mg_q4k_x_to_limbs_on_stream(x, blocks_per_row * 256, records, stream);
     if (rc) return rc;
-    return dispatch_dp4a<0>(w_q4, dev_ptr[dev], nullptr, y, out_dim, blocks_per_row, peer, (cudaStream_t)stream);
+    return dispatch_dp4a<0>(w_q4, records, nullptr, y, out_dim, blocks_per_row, peer, (cudaStream_t)stream);
 }
 
 extern "C" int launch_matvec_q4k_on_stream(const uint8_t* w_q4, const float* x, float* y, int out_dim,

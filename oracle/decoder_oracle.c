@@ -59,10 +59,13 @@ void orc_apply_rope(float* data, int pos, int n_heads, int head_dim, float base)
     }
 }
 
-/* llm.rs:986-1032 over a half-precision cache laid out [seq][kv_dim] (token-major). */
+/* llm.rs:986-1032 over a cache laid out [seq][kv_dim] (token-major): half precision (k_buf / v_buf,
+ * the 7B-class configuration of this build) or f32 (k32 / v32, what the reference itself keeps:
+ * llm.rs:305-310, :1232-1234). */
 typedef struct {
     const float* q; const uint16_t* k_buf; const uint16_t* v_buf; float* out;
     int seq_len, n_heads, n_kv_heads, head_dim;
+    const float* k32; const float* v32;
 } orc_att_ctx;
 static void orc_att_range(int h0, int h1, void* p) {
     orc_att_ctx* c = (orc_att_ctx*)p;
@@ -76,9 +79,14 @@ static void orc_att_range(int h0, int h1, void* p) {
         const float* qh = c->q + (size_t)h * head_dim;
         size_t kv_off = (size_t)kv_h * head_dim;
         for (int t = 0; t < seq_len; ++t) {
-            const uint16_t* kt = c->k_buf + (size_t)t * kv_dim + kv_off;
             float s = 0.0f;
-            for (int i = 0; i < head_dim; ++i) s += qh[i] * orc_f16_to_f32(kt[i]);
+            if (c->k32) {
+                const float* kt = c->k32 + (size_t)t * kv_dim + kv_off;
+                for (int i = 0; i < head_dim; ++i) s += qh[i] * kt[i];
+            } else {
+                const uint16_t* kt = c->k_buf + (size_t)t * kv_dim + kv_off;
+                for (int i = 0; i < head_dim; ++i) s += qh[i] * orc_f16_to_f32(kt[i]);
+            }
             scores[t] = s * scale;
         }
         float mx = -INFINITY;
@@ -89,16 +97,26 @@ static void orc_att_range(int h0, int h1, void* p) {
         float* dst = c->out + (size_t)h * head_dim;
         for (int i = 0; i < head_dim; ++i) dst[i] = 0.0f;
         for (int t = 0; t < seq_len; ++t) {
-            const uint16_t* vt = c->v_buf + (size_t)t * kv_dim + kv_off;
             float pr = scores[t];
-            for (int i = 0; i < head_dim; ++i) dst[i] += pr * orc_f16_to_f32(vt[i]);
+            if (c->v32) {
+                const float* vt = c->v32 + (size_t)t * kv_dim + kv_off;
+                for (int i = 0; i < head_dim; ++i) dst[i] += pr * vt[i];
+            } else {
+                const uint16_t* vt = c->v_buf + (size_t)t * kv_dim + kv_off;
+                for (int i = 0; i < head_dim; ++i) dst[i] += pr * orc_f16_to_f32(vt[i]);
+            }
         }
     }
     free(scores);
 }
 void orc_attention_f16kv(const float* q, const uint16_t* k_buf, const uint16_t* v_buf, float* out,
                          int seq_len, int n_heads, int n_kv_heads, int head_dim) {
-    orc_att_ctx c = { q, k_buf, v_buf, out, seq_len, n_heads, n_kv_heads, head_dim };
+    orc_att_ctx c = { q, k_buf, v_buf, out, seq_len, n_heads, n_kv_heads, head_dim, 0, 0 };
+    orc_parallel_for(n_heads, orc_att_range, &c, 0);
+}
+void orc_attention_f32kv(const float* q, const float* k_buf, const float* v_buf, float* out,
+                         int seq_len, int n_heads, int n_kv_heads, int head_dim) {
+    orc_att_ctx c = { q, 0, 0, out, seq_len, n_heads, n_kv_heads, head_dim, k_buf, v_buf };
     orc_parallel_for(n_heads, orc_att_range, &c, 0);
 }
 
@@ -149,9 +167,9 @@ typedef struct {
 
 /* One token at position `pos` (the number of positions already in the cache).
  * llm.rs:1177-1298.  matvec_mode: 0 scalar f32, 1 reference selector, 2 f64. */
-void orc_forward_token(const orc_decoder_cfg* cfg, const orc_decoder_layer* layers,
-                       const uint16_t* embed, const uint16_t* lm_head, const float* out_norm_w,
-                       int pos, uint32_t token, float* logits, int matvec_mode) {
+static void forward_token_impl(const orc_decoder_cfg* cfg, const orc_decoder_layer* layers, float* const* k32,
+                               float* const* v32, const uint16_t* embed, const uint16_t* lm_head,
+                               const float* out_norm_w, int pos, uint32_t token, float* logits, int matvec_mode) {
     int D = cfg->d_model, H = cfg->n_heads, KVH = cfg->n_kv_heads, hd = cfg->head_dim;
     int q_dim = H * hd, kv_dim = KVH * hd, F = cfg->d_ff;
     float* hidden = (float*)malloc(sizeof(float) * D);
@@ -174,11 +192,19 @@ void orc_forward_token(const orc_decoder_cfg* cfg, const orc_decoder_layer* laye
         orc_matvec_q4k(L->wv, cur, v, kv_dim, D / 256, matvec_mode, 0);
         orc_apply_rope(q, pos, H, hd, cfg->rope_base);
         orc_apply_rope(k, pos, KVH, hd, cfg->rope_base);
-        for (int i = 0; i < kv_dim; ++i) {
-            L->k_cache[(size_t)pos * kv_dim + i] = orc_f32_to_f16_rne(k[i]);
-            L->v_cache[(size_t)pos * kv_dim + i] = orc_f32_to_f16_rne(v[i]);
+        if (k32) {  /* the reference's own cache: f32, appended unrounded (llm.rs:1232-1234) */
+            for (int i = 0; i < kv_dim; ++i) {
+                k32[l][(size_t)pos * kv_dim + i] = k[i];
+                v32[l][(size_t)pos * kv_dim + i] = v[i];
+            }
+            orc_attention_f32kv(q, k32[l], v32[l], att, pos + 1, H, KVH, hd);
+        } else {
+            for (int i = 0; i < kv_dim; ++i) {
+                L->k_cache[(size_t)pos * kv_dim + i] = orc_f32_to_f16_rne(k[i]);
+                L->v_cache[(size_t)pos * kv_dim + i] = orc_f32_to_f16_rne(v[i]);
+            }
+            orc_attention_f16kv(q, L->k_cache, L->v_cache, att, pos + 1, H, KVH, hd);
         }
-        orc_attention_f16kv(q, L->k_cache, L->v_cache, att, pos + 1, H, KVH, hd);
         orc_matvec_q4k(L->wo, att, tmp, D, q_dim / 256, matvec_mode, 0);
         for (int i = 0; i < D; ++i) hidden[i] += tmp[i];
         orc_rms_norm(hidden, L->ffn_norm, cur, D, cfg->rms_eps);
@@ -192,4 +218,18 @@ void orc_forward_token(const orc_decoder_cfg* cfg, const orc_decoder_layer* laye
     orc_matvec_f16(lm_head, cur, logits, cfg->vocab, D);
 
     free(hidden); free(cur); free(q); free(k); free(v); free(att); free(tmp); free(gate); free(up);
+}
+
+/* Half-precision KV cache: the 7B-class configuration this build benchmarks. */
+void orc_forward_token(const orc_decoder_cfg* cfg, const orc_decoder_layer* layers,
+                       const uint16_t* embed, const uint16_t* lm_head, const float* out_norm_w,
+                       int pos, uint32_t token, float* logits, int matvec_mode) {
+    forward_token_impl(cfg, layers, 0, 0, embed, lm_head, out_norm_w, pos, token, logits, matvec_mode);
+}
+/* f32 KV cache, as the reference keeps it (llm.rs:305-310): k32[l] / v32[l] are [max_seq][kv_dim] floats;
+ * the half caches inside `layers` are not touched. */
+void orc_forward_token_f32kv(const orc_decoder_cfg* cfg, const orc_decoder_layer* layers, float* const* k32,
+                             float* const* v32, const uint16_t* embed, const uint16_t* lm_head,
+                             const float* out_norm_w, int pos, uint32_t token, float* logits, int matvec_mode) {
+    forward_token_impl(cfg, layers, k32, v32, embed, lm_head, out_norm_w, pos, token, logits, matvec_mode);
 }

@@ -75,6 +75,7 @@ class OracleLib:
         c.orc_argmax.restype = C.c_uint32
         c.orc_argmax.argtypes = [C.c_void_p, C.c_int]
         c.orc_forward_token.argtypes = [C.c_void_p] * 5 + [C.c_int, C.c_uint32, C.c_void_p, C.c_int]
+        c.orc_forward_token_f32kv.argtypes = [C.c_void_p] * 7 + [C.c_int, C.c_uint32, C.c_void_p, C.c_int]
 
     # ---- format -----------------------------------------------------------------------
     def f16_to_f32(self, h: int) -> float:
@@ -201,6 +202,18 @@ class OracleLib:
         logits = np.empty(cfg.vocab, dtype=np.float32)
         self.c.orc_forward_token(C.byref(cfg), arr, _p(embed), _p(lm_head), _p(out_norm), pos, token,
                                  _p(logits), mode)
+        return logits
+
+    def forward_token_f32kv(self, cfg: DecoderCfg, layers, k32, v32, embed, lm_head, out_norm, pos, token,
+                            mode: int = MODE_F64) -> np.ndarray:
+        """The reference's own arrangement: f32 KV caches (k32[l], v32[l]: [max_seq * kv_dim] f32 arrays,
+        appended unrounded, crates/modgrad-device/src/kfd/llm.rs:305-310, :1232-1234)."""
+        arr = (DecoderLayer * len(layers))(*layers)
+        kp = (C.c_void_p * len(k32))(*[a.ctypes.data for a in k32])
+        vp_ = (C.c_void_p * len(v32))(*[a.ctypes.data for a in v32])
+        logits = np.empty(cfg.vocab, dtype=np.float32)
+        self.c.orc_forward_token_f32kv(C.byref(cfg), arr, kp, vp_, _p(embed), _p(lm_head), _p(out_norm), pos, token,
+                                       _p(logits), mode)
         return logits
 
 

@@ -103,7 +103,9 @@ def kat_one_hot():
         where[e] = v
     exp = [(Fraction(where.get(e, 0)), False) for e in range(256)]
     assert exp == expected_block(0x3C00, 0x0000, UNIT_SC, UNIT_M, qs)
-    return dict(name="one_hot_unit_scales", block=block(0x3C00, 0, UNIT_SCALES, qs), expected=exp)
+    return dict(name="one_hot_unit_scales", block=block(0x3C00, 0, UNIT_SCALES, qs), expected=exp,
+                derived_from="element order: kfd/gguf.rs:376-402; the same order in kernels/matvec_q4k.hip:13-18, :87-89 and "
+                             "kfd/kernels/matvec_q4k.s:45-57")
 
 
 def kat_scale_unpack():
@@ -114,7 +116,9 @@ def kat_scale_unpack():
     qs = [(i * 7 + 1) & 0xFF for i in range(128)]
     exp = expected_block(0x4000, 0x3800, MIXED_SC, MIXED_M, qs)  # d = 2.0, dmin = 0.5
     return dict(name="mixed_scales_affine", block=block(0x4000, 0x3800, MIXED_SCALES, qs), expected=exp,
-                sc=MIXED_SC, m=MIXED_M)
+                sc=MIXED_SC, m=MIXED_M,
+                derived_from="six-bit unpack: kfd/gguf.rs:334-342 (device copy kernels/matvec_q4k.hip:41-53); affine "
+                             "dequantisation: kfd/gguf.rs:386-398")
 
 
 def kat_all_ones_header():
@@ -122,7 +126,7 @@ def kat_all_ones_header():
     qs = [0xF0 if i % 2 else 0x0F for i in range(128)]
     exp = expected_block(0x3400, 0x3000, [63] * 8, [63] * 8, qs)  # d = 0.25, dmin = 0.125
     return dict(name="all_ones_header", block=block(0x3400, 0x3000, [0xFF] * 12, qs), expected=exp,
-                sc=[63] * 8, m=[63] * 8)
+                sc=[63] * 8, m=[63] * 8, derived_from="kfd/gguf.rs:334-342 (every field 63), :386-398")
 
 
 def kat_specials():
@@ -136,7 +140,8 @@ def kat_specials():
         ("dmin_subnormal", 0x3C00, 0x0200), ("d_neg_zero", 0x8000, 0x3C00), ("d_max_half", 0x7BFF, 0x0000),
     ]:
         exp = expected_block(d_bits, dmin_bits, MIXED_SC, MIXED_M, qs)
-        cases.append(dict(name="special_" + name, block=block(d_bits, dmin_bits, MIXED_SCALES, qs), expected=exp))
+        cases.append(dict(name="special_" + name, block=block(d_bits, dmin_bits, MIXED_SCALES, qs), expected=exp,
+                          derived_from="half decode kfd/gguf.rs:281-292; non-finite scales become 0: kfd/gguf.rs:371-372"))
     return cases
 
 
@@ -147,6 +152,7 @@ def main():
         exp = k["expected"]
         rec = dict(name=k["name"], block_hex=bytes(k["block"]).hex(),
                    expected_f32_bits=[f32_bits(v, nz) for v, nz in exp])
+        rec["derived_from"] = k["derived_from"]   # the reference lines this expectation follows
         if "sc" in k:
             rec["sc"], rec["m"] = k["sc"], k["m"]
         # matvec known answers with integer activations: x[e] = (e % 7) - 3 and a one-hot

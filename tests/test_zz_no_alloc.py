@@ -37,6 +37,26 @@ def test_noalloc_matvec_matches_ordinary_entry_point_twice_in_a_row(cuda):
             assert rel_rms_err(b, a.astype(np.float64)) <= GEMV_TOL, (out_dim, bpr, call)
 
 
+def test_noalloc_calls_queued_back_to_back_share_the_array_safely(cuda):
+    """Three calls queued on one stream with no synchronisation in between, each with its own x and y:
+    every kernel waits for its predecessor to complete before it rewrites the shared array, so each
+    result must equal the ordinary entry point's."""
+    out_dim, bpr = 2048, 40
+    rng = np.random.Generator(np.random.PCG64(17))
+    wd = up(synth.q4k_matrix(out_dim, bpr * 256, rng))
+    xs = [up(synth.activations(bpr * 256, rng)) for _ in range(3)]
+    ys = [DeviceBuffer(out_dim * 4) for _ in range(3)]
+    refs = [DeviceBuffer(out_dim * 4) for _ in range(3)]
+    for x, y in zip(xs, ys):
+        assert cuda.launch_matvec_q4k_noalloc_on_stream(wd.ptr, x.ptr, y.ptr, out_dim, bpr, None) == 0
+    for x, r in zip(xs, refs):
+        assert cuda.launch_matvec_q4k_on_stream(wd.ptr, x.ptr, r.ptr, out_dim, bpr, None) == 0
+    kern.sync()
+    for y, r in zip(ys, refs):
+        assert rel_rms_err(y.copy_to_host(out_dim), r.copy_to_host(out_dim).astype(np.float64)) <= GEMV_TOL
+    assert cuda.mg_matvec_q4k_timeouts() == 0
+
+
 def test_noalloc_matvec_refuses_rows_beyond_its_capacity(cuda):
     buf = DeviceBuffer(4096)
     assert cuda.launch_matvec_q4k_noalloc_on_stream(buf.ptr, buf.ptr, buf.ptr, 4, 129, None) == 1
