@@ -446,9 +446,9 @@ def main():
 
 def matmul_leg(args, torch, lib, dev):
     """Multi-sequence dequant-GEMM on the tensor cores (tcgen05 + TMEM): M in {16, 32, 64}
-    activation rows (N(0,1), half precision by contract) times Q4_K W of 18944x3584 and 3584x18944.
+    activation rows (N(0,1), f32 in, carried as two half limbs) times Q4_K W of 18944x3584 and 3584x18944.
     Weights rotate through 4 copies (153 MB > L2).  Device time per launch incl. the activation
-    tile preparation kernels; GB/s counts the weight bytes, TFLOP/s counts 2*M*N*K."""
+    slab preparation kernels; GB/s counts the weight bytes, TFLOP/s counts 2*M*N*K."""
     peak_bw, kind = measured_peak()
     out = {}
     st = torch.cuda.Stream()

@@ -47,6 +47,7 @@
 #include "gemv_q4k_device.cuh"
 #include "launch_common.cuh"
 #include "q4k_device.cuh"
+#include "tensor_map.hpp"
 
 namespace gemvmma {
 
@@ -679,21 +680,8 @@ bool pick_config(int bpr, int budget, int max_tiles, Config& best) {
     return false;
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-// cuTensorMapEncodeTiled through the runtime (the library does not link libcuda).
-EncodeTiledFn encode_tiled() {
-    static const EncodeTiledFn fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
+using mg::encode_tiled;
+using mg::EncodeTiledFn;
 
 }  // namespace
 
