@@ -19,23 +19,23 @@
 //
 // One CTA per SM walks work items (128 output rows x a range of super-blocks); the pipeline runs
 // across item boundaries.  Warps:
-//   0-15   producers, thread = (row, 32-byte group of the super-block).  The raw 18 KiB of a
+//   12-27  producers, thread = (row, 32-byte group of the super-block).  The raw 18 KiB of a
 //          128-row super-block column arrive by ONE 2-D tensor-map TMA load into a ring of raw
 //          stages; a producer reads its row's header and group from there, unpacks nibbles and
 //          6-bit scales in registers, forms sc*q as f16 pairs (one HFMA2 per two weights) and
 //          writes a 64-deep slab of the 128-byte-swizzled K-major A ring.  One producer group per
 //          block also writes the block's eight mins (A2) and its d/dmin pair for the drain.
-//   16-23  drain warps, thread = (row, half of the sequences): tcgen05.ld of the block's
+//   4-11   drain warps, thread = (row, half of the sequences): tcgen05.ld of the block's
 //          accumulators, acc += d * (hi + 2^-11 lo) - dmin * D2, store at the end of the item.
-//   24-25  one thread each issues tcgen05.mma (A, B from shared memory through matrix descriptors,
+//   0-1    one thread each issues tcgen05.mma (A, B from shared memory through matrix descriptors,
 //          D in TMEM) for the super-blocks of its accumulator set, even or odd: block b+1
 //          multiplies while b drains, and two issuers keep the tensor pipe fed (a lone thread
 //          issues one 16-deep step per ~55 cycles, two reach ~40 in aggregate; the steps are small
 //          because N is small).  Stages are released in pairs: a tcgen05.commit costs a step's
 //          worth of issue time.
-//   26     one thread issues the raw-weight TMA loads (before the kernel waits for its
+//   2      one thread issues the raw-weight TMA loads (before the kernel waits for its
 //          predecessor in the stream: weights are never produced by the activation kernels).
-//   27     one thread brings the prepared activation slabs in with 1-D bulk copies.
+//   3      one thread brings the prepared activation slabs in with 1-D bulk copies.
 // Every mbarrier wait is bounded: on expiry an error word is set, the CTA stops issuing, waits
 // (bounded) for the copies it has in flight, frees its TMEM and returns; the host reports
 // cudaErrorLaunchTimeout.
@@ -53,9 +53,11 @@ constexpr int kRawBytes = kRows * q4k::kBlockBytes;  // one super-block column o
 constexpr int kParts = 4;                 // producer groups: one per 32-byte group (64 weights) of a super-block
 constexpr int kProducerWarps = kParts * (kRows / 32);   // 16
 constexpr int kDrainWarps = 8;
-constexpr int kMmaWarp = kProducerWarps + kDrainWarps;  // 24, 25: one issuer per accumulator set
-constexpr int kRawWarp = kMmaWarp + 2, kActWarp = kMmaWarp + 3;
-constexpr int kThreads = (kActWarp + 1) * 32;           // 896
+// Warp roles by index.
+constexpr int kMmaWarp = 0, kRawWarp = 1, kActWarp = 2;
+constexpr int kDrainWarp0 = 3;                          // 3..10; warp index mod 4 = TMEM lane quadrant
+constexpr int kProducerWarp0 = kDrainWarp0 + kDrainWarps;  // 11..26
+constexpr int kThreads = (kProducerWarp0 + kProducerWarps) * 32;  // 864
 constexpr int kDdDepth = 4;               // blocks whose d/dmin pairs are kept for the drain
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr size_t kTailBytes = 1024;  // scratch tail: error word, row maxima, flags, row scales (256 B each)
@@ -97,6 +99,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile
     }
     *abort_flag = 1;
     return false;
+}
+// The same for a whole converged warp: every lane polls, the verdict is made uniform.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* b, uint32_t parity, volatile int* abort_flag) {
+    return __all_sync(0xFFFFFFFFu, mbar_wait(b, parity, abort_flag));
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -146,7 +161,17 @@ __device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t (&v)[8]) {
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                  : "r"(addr));
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// tcgen05.wait::ld with the loaded registers as in/out operands: without that tie the compiler is
+// free to schedule arithmetic on the registers above the wait (it only orders volatile asm
+// statements among themselves), and the values would be read before the asynchronous load lands.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&a)[8], uint32_t (&b)[8], uint32_t (&c)[8]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]),
+                   "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]),
+                   "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]), "+r"(c[4]), "+r"(c[5]), "+r"(c[6]), "+r"(c[7])
+                 :
+                 : "memory");
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -268,13 +293,14 @@ struct Params {
 template <int M>
 struct Ctl {
     uint64_t raw_full[Depth<M>::kRaw], raw_empty[Depth<M>::kRaw];
-    uint64_t full[Depth<M>::kStages];       // quarter stage filled (producer group + activation slab)
-    uint64_t empty[Depth<M>::kStages / 2];  // a PAIR of quarter stages released by one tcgen05.commit
+    // A/B stages are handed over in PAIRS of quarter stages (half a super-block): every barrier
+    // round trip costs the issuing warp instructions, and it is the pipeline's narrowest point.
+    uint64_t full[Depth<M>::kStages / 2];   // pair filled: eight producer warps + the activation slabs
+    uint64_t empty[Depth<M>::kStages / 2];  // pair released by one tcgen05.commit
     uint64_t full2[2];                      // A2/B2 of accumulator set t filled
     uint64_t d_full[2], d_free[2];          // accumulator set t: MMAs done (A2/B2 free again) / drained
     uint32_t tmem_base;
     int abort_flag;
-    uint32_t full_seen;  // blocks whose `full` waits an issuer has passed (hand-off between the two issuers)
 };
 
 template <int M>
@@ -325,15 +351,16 @@ matmul_q4k_tc_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) {
             mbar_init(&ctl->raw_full[i], 1);
             mbar_init(&ctl->raw_empty[i], kProducerWarps);
         }
-        for (int i = 0; i < S; ++i) mbar_init(&ctl->full[i], kRows / 32 + 1);  // four producer warps + the bulk copy's arrive
-        for (int i = 0; i < P; ++i) mbar_init(&ctl->empty[i], 1);
+        for (int i = 0; i < P; ++i) {
+            mbar_init(&ctl->full[i], 2 * (kRows / 32) + 1);  // the warps of two producer groups + the bulk copies' arrive
+            mbar_init(&ctl->empty[i], 1);
+        }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&ctl->full2[i], kRows / 32 + 1);
             mbar_init(&ctl->d_full[i], 1);
             mbar_init(&ctl->d_free[i], kDrainWarps);
         }
         ctl->abort_flag = 0;
-        ctl->full_seen = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == kMmaWarp) {
@@ -353,10 +380,10 @@ matmul_q4k_tc_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) {
     volatile int* abort_flag = &ctl->abort_flag;
     const int grid = (int)gridDim.x;
 
-    if (warp < kProducerWarps) {
+    if (warp >= kProducerWarp0) {
         // ================= producers: thread = (row of the tile, 32-byte group) =========================
-        const int part = warp >> 2;
-        const int r = (warp & 3) * 32 + lane;
+        const int part = (warp - kProducerWarp0) >> 2;
+        const int r = ((warp - kProducerWarp0) & 3) * 32 + lane;
         // byte offsets of this row's eight 16-byte chunks inside a slab (128-byte swizzle)
         const uint32_t row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128), rx = (uint32_t)(r & 7) << 4;
         const uint32_t sA_addr = smem_u32(sA) + row_off;
@@ -413,7 +440,7 @@ matmul_q4k_tc_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) {
                     }
                     fence_proxy_async();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&ctl->full[s]);
+                    if (lane == 0) mbar_arrive(&ctl->full[pr]);
                 }
                 // ---- A2 (the eight 6-bit mins, each three times: one per limb of sum(x)) and the block's
                 //      d/dmin pair, by the producer group whose turn it is ------------------------------------
@@ -441,10 +468,10 @@ matmul_q4k_tc_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) {
                 }
             }
         }
-    } else if (warp < kMmaWarp) {
+    } else if (warp >= kDrainWarp0) {
         // ================= drain: thread = (row, half of the sequences) ====================================
         constexpr int MH = M / 2;
-        const int dw = warp - kProducerWarps;
+        const int dw = warp - kDrainWarp0;
         const int quad = warp & 3;       // TMEM lanes 32*quad .. (a warp reaches the quadrant warp_id % 4)
         const int half_id = dw >> 2;
         const int r = quad * 32 + lane;
@@ -472,7 +499,7 @@ matmul_q4k_tc_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) {
                     tmem_ld8(lane_base + t * N + col, vh);
                     tmem_ld8(lane_base + t * N + M + col, vl);
                     tmem_ld8(lane_base + 2 * N + t * M + col, v2);
-                    tmem_ld_wait();
+                    tmem_ld_wait(vh, vl, v2);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const float v = fmaf(__uint_as_float(vl[i]), 1.0f / 2048.0f, __uint_as_float(vh[i]));
@@ -501,57 +528,58 @@ matmul_q4k_tc_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) {
                 acc[i] = 0.0f;
             }
         }
-    } else if (warp < kRawWarp) {
-        // ================= MMA issuers: warp kMmaWarp + t owns accumulator set t (blocks gb = t mod 2) ========
-        // A parity wait is only sound for a thread that has seen every earlier phase of the barrier
-        // complete.  The `full` barriers serve both issuers in turn, so an issuer starts on block gb
-        // only after the other one has passed all its `full` waits of block gb - 1 (full_seen): the
-        // hand-off leaves the owner's last four steps, the min-term steps and the commits to overlap
-        // with the successor's waits and first steps.
-        if (lane == 0) {
+    } else if (warp == kMmaWarp) {
+        // ================= MMA issuer ========================================================================
+        // The whole warp walks the loop and waits on the barriers, so that the index arithmetic stays in
+        // the uniform datapath; one elected lane issues the tensor-core instructions.  (Issuing from two
+        // warps, one per accumulator set, corrupted results at N = 128: one issuer only.)
+        {
             constexpr uint32_t idesc = idesc_f16(N), idesc2 = idesc_f16(M);
-            const uint32_t t = (uint32_t)(warp - kMmaWarp);
             const uint32_t a_lo0 = smem_desc_lo(smem_u32(sA)), b_lo0 = smem_desc_lo(smem_u32(sB));
-            const uint32_t a2_lo = smem_desc_lo(smem_u32(sA2) + t * 64), b2_lo = smem_desc_lo(smem_u32(sB2 + t * L::kB2Bytes));
-            const uint32_t d1 = tmem + t * N, d2 = tmem + 2 * N + t * M;
-            volatile uint32_t* full_seen = &ctl->full_seen;
+            const uint32_t a2_lo0 = smem_desc_lo(smem_u32(sA2)), b2_lo0 = smem_desc_lo(smem_u32(sB2));
             uint32_t gb = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < p.n_items && ok; item += grid) {
                 int tile, blk0, n_blk;
                 item_range(p, item, tile, blk0, n_blk);
                 for (int b = 0; b < n_blk && ok; ++b, ++gb) {
-                    if ((gb & 1u) != t) continue;
-                    ok = mbar_wait(&ctl->d_free[t], ((gb >> 1) & 1u) ^ 1u, abort_flag);  // accumulators drained
-                    if (!ok) break;
-                    for (uint32_t i = 0; *full_seen < gb; ++i) {
-                        if (i >= kSpinLimit) *abort_flag = 1;
-                        if (*abort_flag) { ok = false; break; }
-                    }
+                    const uint32_t t = gb & 1u;
+                    const uint32_t d1 = tmem + t * N, d2 = tmem + 2 * N + t * M;
+                    ok = mbar_wait_warp(&ctl->d_free[t], ((gb >> 1) & 1u) ^ 1u, abort_flag);  // accumulators drained
                     if (!ok) break;
 #pragma unroll
-                    for (uint32_t q = 0; q < 4; ++q) {
-                        const uint32_t it = 4u * gb + q, s = it % S;
-                        ok = mbar_wait(&ctl->full[s], (it / S) & 1u, abort_flag);
+                    for (uint32_t h = 0; h < 2; ++h) {
+                        const uint32_t u = 2u * gb + h, pr = u % P;
+                        ok = mbar_wait_warp(&ctl->full[pr], (u / P) & 1u, abort_flag);
                         if (!ok) break;
-                        if (q == 3) {
-                            ok = mbar_wait(&ctl->full2[t], (gb >> 1) & 1u, abort_flag);
-                            if (!ok) break;
-                            *full_seen = gb + 1;
-                        }
                         tc_fence_after();
-                        const uint32_t a_lo = a_lo0 + s * (kSlabBytes >> 4), b_lo = b_lo0 + s * (L::kBStage >> 4);
-                        if (q == 0) umma_f16<false>(d1, a_lo, b_lo, kDescHi, idesc);
-                        else umma_f16<true>(d1, a_lo, b_lo, kDescHi, idesc);
-                        umma_f16<true>(d1, a_lo + 2, b_lo + 2, kDescHi, idesc);  // 16 weights = 32 bytes along the swizzled row
-                        umma_f16<true>(d1, a_lo + 4, b_lo + 4, kDescHi, idesc);
-                        umma_f16<true>(d1, a_lo + 6, b_lo + 6, kDescHi, idesc);
-                        if (q & 1u) umma_commit(&ctl->empty[(it >> 1) % P]);
+                        // the pair's two slabs lie back to back: eight 16-deep steps
+                        const uint32_t a_lo = a_lo0 + pr * (2 * kSlabBytes >> 4), b_lo = b_lo0 + pr * (2 * L::kBStage >> 4);
+                        if (elect_one()) {
+#pragma unroll
+                            for (uint32_t j = 0; j < 2; ++j) {
+                                const uint32_t aj = a_lo + j * (kSlabBytes >> 4), bj = b_lo + j * (L::kBStage >> 4);
+                                if (h == 0 && j == 0) umma_f16<false>(d1, aj, bj, kDescHi, idesc);
+                                else umma_f16<true>(d1, aj, bj, kDescHi, idesc);
+                                umma_f16<true>(d1, aj + 2, bj + 2, kDescHi, idesc);  // 16 weights = 32 bytes along the swizzled row
+                                umma_f16<true>(d1, aj + 4, bj + 4, kDescHi, idesc);
+                                umma_f16<true>(d1, aj + 6, bj + 6, kDescHi, idesc);
+                            }
+                            umma_commit(&ctl->empty[pr]);
+                        }
+                        __syncwarp();
                     }
                     if (!ok) break;
-                    umma_f16<false>(d2, a2_lo, b2_lo, kDescHi, idesc2);  // 24 live k values: two 16-deep steps
-                    umma_f16<true>(d2, a2_lo + 2, b2_lo + 2, kDescHi, idesc2);
-                    umma_commit(&ctl->d_full[t]);
+                    ok = mbar_wait_warp(&ctl->full2[t], (gb >> 1) & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (elect_one()) {
+                        const uint32_t a2_lo = a2_lo0 + t * (64 >> 4), b2_lo = b2_lo0 + t * (L::kB2Bytes >> 4);
+                        umma_f16<false>(d2, a2_lo, b2_lo, kDescHi, idesc2);  // 24 live k values: two 16-deep steps
+                        umma_f16<true>(d2, a2_lo + 2, b2_lo + 2, kDescHi, idesc2);
+                        umma_commit(&ctl->d_full[t]);
+                    }
+                    __syncwarp();
                 }
             }
         }
@@ -578,7 +606,7 @@ matmul_q4k_tc_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) {
                 }
             }
         }
-    } else {
+    } else if (warp == kActWarp) {
         // ================= activation-slab loader =========================================================
         if (lane == 0) {
             asm volatile("griddepcontrol.wait;" ::: "memory");  // the slabs come from the kernel launched just before
@@ -588,15 +616,14 @@ matmul_q4k_tc_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) {
                 int tile, blk0, n_blk;
                 item_range(p, item, tile, blk0, n_blk);
                 for (int b = 0; b < n_blk && ok; ++b, ++gb) {
-                    for (uint32_t q = 0; q < 4; ++q) {
-                        const uint32_t it = 4u * gb + q, s = it % S;
-                        if ((q & 1u) == 0) {
-                            ok = mbar_wait(&ctl->empty[(it >> 1) % P], (((it >> 1) / P) & 1u) ^ 1u, abort_flag);
-                            if (!ok) break;
-                        }
-                        mbar_arrive_expect_tx(&ctl->full[s], L::kBStage);
-                        bulk_copy_g2s(sB + s * L::kBStage, p.b_img + ((size_t)(blk0 + b) * 4 + q) * L::kBStage, L::kBStage,
-                                      &ctl->full[s]);
+                    for (uint32_t h = 0; h < 2; ++h) {
+                        const uint32_t u = 2u * gb + h, pr = u % P;
+                        ok = mbar_wait(&ctl->empty[pr], ((u / P) & 1u) ^ 1u, abort_flag);
+                        if (!ok) break;
+                        // the two quarter slabs of a half block are contiguous in the image and in the ring
+                        mbar_arrive_expect_tx(&ctl->full[pr], 2 * L::kBStage);
+                        bulk_copy_g2s(sB + pr * (2 * L::kBStage), p.b_img + ((size_t)(blk0 + b) * 2 + h) * (2 * L::kBStage),
+                                      2 * L::kBStage, &ctl->full[pr]);
                     }
                     if (!ok) break;
                     const uint32_t t = gb & 1u;
