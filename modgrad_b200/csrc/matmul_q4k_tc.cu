@@ -19,26 +19,31 @@
 //
 // One CTA per SM walks work items (128 output rows x a range of super-blocks); the pipeline runs
 // across item boundaries.  Warps:
-//   12-27  producers, thread = (row, 32-byte group of the super-block).  The raw 18 KiB of a
-//          128-row super-block column arrive by ONE 2-D tensor-map TMA load into a ring of raw
-//          stages; a producer reads its row's header and group from there, unpacks nibbles and
-//          6-bit scales in registers, forms sc*q as f16 pairs (one HFMA2 per two weights) and
-//          writes a 64-deep slab of the 128-byte-swizzled K-major A ring.  One producer group per
-//          block also writes the block's eight mins (A2) and its d/dmin pair for the drain.
-//   4-11   drain warps, thread = (row, half of the sequences): tcgen05.ld of the block's
+//   0      MMA issuer.  The whole warp walks the loop and waits on the barriers (the index
+//          arithmetic then stays in the uniform datapath); one elected lane issues tcgen05.mma (A, B
+//          from shared memory through matrix descriptors, D in TMEM, two accumulator sets so that
+//          block b+1 multiplies while b drains) and tcgen05.commit onto mbarriers.  A 16-deep step
+//          of 128 rows takes the tensor pipe ~55 cycles whatever N <= 128 is, so the pipe's own
+//          floor is ~1000 cycles per super-block.  One issuer only: with a second issuing warp
+//          (one per accumulator set) results were corrupted at N = 128.
+//   1      one thread issues the raw-weight TMA loads: ONE 2-D tensor-map box (128 rows x 144
+//          bytes) per super-block into a ring of raw stages, started before the kernel waits for
+//          its predecessor in the stream (weights are never produced by the activation kernels).
+//   2      one thread brings the prepared activation slabs in with 1-D bulk copies.
+//   3-10   drain warps, thread = (row, half of the sequences): tcgen05.ld of the block's
 //          accumulators, acc += d * (hi + 2^-11 lo) - dmin * D2, store at the end of the item.
-//   0-1    one thread each issues tcgen05.mma (A, B from shared memory through matrix descriptors,
-//          D in TMEM) for the super-blocks of its accumulator set, even or odd: block b+1
-//          multiplies while b drains, and two issuers keep the tensor pipe fed (a lone thread
-//          issues one 16-deep step per ~55 cycles, two reach ~40 in aggregate; the steps are small
-//          because N is small).  Stages are released in pairs: a tcgen05.commit costs a step's
-//          worth of issue time.
-//   2      one thread issues the raw-weight TMA loads (before the kernel waits for its
-//          predecessor in the stream: weights are never produced by the activation kernels).
-//   3      one thread brings the prepared activation slabs in with 1-D bulk copies.
-// Every mbarrier wait is bounded: on expiry an error word is set, the CTA stops issuing, waits
-// (bounded) for the copies it has in flight, frees its TMEM and returns; the host reports
-// cudaErrorLaunchTimeout.
+//   11-26  producers, thread = (row, 32-byte group of the super-block): read the row's header and
+//          group from the raw stage, unpack nibbles and 6-bit scales in registers, form sc*q as
+//          f16 pairs (one HFMA2 per two weights; high nibbles are used in place as 16 q with the
+//          scale divided by 16) and write one 64-deep slab row of the 128-byte-swizzled K-major A
+//          ring.  One producer group per block also writes the block's eight mins (A2) and its
+//          d/dmin pair for the drain.
+// A/B stages are quarter super-blocks handed over in pairs.  A parity wait is only sound for a
+// waiter that cannot be two phases away from the barrier: most waiters see every phase of their
+// barriers in order; where the producers do not (`empty` with three pairs, `d_full`), the ring
+// order bounds the distance (comments at those waits).  Every wait is bounded: on expiry an error word is set, the CTA stops
+// issuing, waits (bounded) for the copies it has in flight, frees its TMEM and returns; the host
+// reports cudaErrorLaunchTimeout.
 #include <cuda_fp16.h>
 
 #include "launch_common.cuh"
@@ -404,6 +409,10 @@ matmul_q4k_tc_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) {
                 const q4k::ScaleMin sm = q4k::unpack_scales(hdr.y, hdr.z, hdr.w);
                 // ---- A: sc*q as f16 for this thread's 64 weights: one slab row -----------------------
                 const uint32_t it = 4u * gb + (uint32_t)part, s = it % S;
+                // Pair use u = it / 2 waits for the release of use u - P.  With three pairs a group meets a
+                // pair only every second use; use u - 2P cannot still be pending then, because the group's
+                // previous fill (use u - 2) waited for the release of u - 2 - P >= u - 2P, and one issuer
+                // releases in order.
                 const uint32_t pr = (it >> 1) % P;
                 ok = mbar_wait(&ctl->empty[pr], (((it >> 1) / P) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
@@ -446,7 +455,10 @@ matmul_q4k_tc_kernel(const Params p, const __grid_constant__ CUtensorMap wmap) {
                 //      d/dmin pair, by the producer group whose turn it is ------------------------------------
                 if ((uint32_t)part == (gb & 3u)) {
                     const uint32_t t2 = gb & 1u;
-                    // set t2 is free again when the MMAs of block gb - 2 have completed
+                    // Set t2 is free again when the MMAs of block gb - 2 have completed.  This group last looked
+                    // at d_full[t2] four blocks ago; block gb - 4 is certainly complete, because the A stage
+                    // this group has just been granted was released by MMAs issued after block gb - 2's
+                    // first pair, and those were issued only after the drain of block gb - 4.
                     ok = mbar_wait(&ctl->d_full[t2], ((gb >> 1) & 1u) ^ 1u, abort_flag);
                     if (!ok) break;
                     uint32_t h[8];  // half bits of the mins: 0x6400 | m is 1024 + m
