@@ -160,7 +160,8 @@ def run_reference(args):
         "config": {"workload": WORKLOAD, "cpu_kernel": kind},
         "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": f"{args.steps} full layer passes (7 matvecs, 131 MB each), "
-                                   f"row-parallel {kind} dot on {cores} threads"},
+                                   f"row-parallel {kind} dot on {cores} threads, rows split statically "
+                                   f"(the reference's rayon splits them dynamically)"},
         "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -185,7 +186,8 @@ def cpu_baseline_sample(budget_s: float = 10.0):
     kind = "avx512" if orc.has_avx512() else "scalar"
     return {"value": round(layer_bytes() * n / dt / 1e9, 3), "unit": "GB/s", "cores": orc.max_threads(),
             "kind": "port",
-            "sample": f"{n} layer passes in {dt:.1f} s, row-parallel {kind} dot (restated reference CPU matvec)"}
+            "sample": f"{n} layer passes in {dt:.1f} s, row-parallel {kind} dot (restated reference CPU matvec), rows "
+                      f"split statically over the threads (the reference's rayon splits them dynamically)"}
 
 
 # ---- our arm ------------------------------------------------------------------------------------
@@ -400,6 +402,14 @@ def main():
     if rank == 0:
         peak, peak_kind = measured_peak()
         per_gpu = value / world
+        dominant = None
+        if "gate_proj" in per_proj and world == 1:
+            gp = per_proj["gate_proj"]
+            dominant = {"kernel": "matvec_q4k_mma_kernel", "projection": "gate_proj",
+                        "bytes_per_launch": synth.gemv_bytes(*LAYER["gate_proj"]), "launch_us": gp["us"],
+                        "achieved": gp["gbs"], "frac": round(gp["gbs"] / peak, 4),
+                        "timing": "CUDA events around a graph of back-to-back launches of this projection "
+                                  "(weight copies rotated), outside the headline region"}
         line = {
             "metric": "q4k_gemv_hbm_gbs", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms / args.steps, 6),
@@ -411,18 +421,26 @@ def main():
             "frac_of_8tbs_nominal": round(per_gpu / 8000.0, 4),
             "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
                          "frac": round(per_gpu / peak, 4),
-                         # dram__bytes_read + write of one gate_proj launch under ncu (38 191 104 B of
-                         # weights): 1.00x the algorithmic bytes; scaled by bytes for the average launch
-                         "traffic": round(layer_bytes_rank(0, world) / 7 * 38_261_760 / 38_281_216),
+                         # NOT measured in this run: dram__bytes_read + write of one gate_proj launch of
+                         # matvec_q4k_mma_kernel under ncu (38 459 648 B against 38 281 216 algorithmic
+                         # bytes, 1.005x), scaled by bytes to the average launch of the layer
+                         "traffic": round(layer_bytes_rank(0, world) / 7 * 38_459_648 / 38_281_216),
+                         "traffic_source": "profiles/gemv_q4k_mma_qwen7b_layer.md (ncu capture of gate_proj), "
+                                           "scaled by algorithmic bytes; not a per-run counter",
                          "peak_source": f"of {peak_kind}",
-                         "kernel": "matvec_q4k_ring_kernel", "bytes_per_launch": layer_bytes_rank(0, world) // 7,
-                         "avg_launch_us": round(ms * 1e3 / (args.steps * 7), 4)},
+                         "kernel": "matvec_q4k_mma_kernel (gate/up, 73 % of the bytes) + matvec_q4k_ring_kernel "
+                                   "(q/k/v/o/down): the timed region is the whole layer",
+                         "bytes_per_launch": layer_bytes_rank(0, world) // 7,
+                         "avg_launch_us": round(ms * 1e3 / (args.steps * 7), 4),
+                         "dominant_kernel": dominant},
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": args.e2e_steps,
                     "call": "mg_buffer_matvec_q4k (HipBuffer::matvec_q4k): pinned host x, host y, 7 calls/step"},
             # six projections are one kernel each; down_proj (rows of 18944) is two
             "gpu_launches": args.steps * 8,
-            "kernels_per_matvec": "matvec_q4k_ring_kernel; x_to_limbs_kernel in front of it for rows over 8192 weights",
+            "kernels_per_matvec": "matvec_q4k_mma_kernel for matrices of >= 4736 rows whose rows fit half an SM's "
+                                  "shared memory (gate/up), else matvec_q4k_ring_kernel, with x_to_limbs_kernel in "
+                                  "front of it for rows over 8192 weights (down)",
             "per_projection": per_proj,
             "grouped": grouped,
             "clocks": clocks,
@@ -500,12 +518,13 @@ def matmul_leg(args, torch, lib, dev):
 
 def layer70b_leg(args, torch, lib, dev, rank, world):
     """A 70B-class decoder layer (hidden 8192, SwiGLU 28672, 64/8 heads of 128): every
-    projection's rows sharded over the ranks, each rank's output slice all-gathered (NCCL over
-    NVLink) before the next projection, the whole pass replayed as one CUDA graph.  At one GPU
+    projection's rows sharded over the ranks, the output slices all-gathered at the four points of
+    the layer where the decode engine exchanges them, the whole pass replayed as one CUDA graph.  At one GPU
     the same layer without the gathers.  Weight copies are rotated so that the per-rank working
     set exceeds L2."""
     import torch.distributed as dist
     layer = synth.LLAMA_70B_LAYER
+    EXCHANGE_AFTER = ("v_proj", "o_proj", "up_proj", "down_proj")
     shard_bytes = sum((shard_rows(o, rank, world)[1] - shard_rows(o, rank, world)[0]) * (i // 256) * 144
                       for o, i in layer.values())
     n_copies = max(2, min(8, -(-400_000_000 // shard_bytes)))
@@ -531,7 +550,7 @@ def layer70b_leg(args, torch, lib, dev, rank, world):
                                                 bpr, s)
             if e:
                 raise RuntimeError(f"launch_matvec_q4k({n}): {lib.mg_get_error_string(e).decode()}")
-            if world > 1:  # in place: this rank's slice already sits at its offset
+            if world > 1 and n in EXCHANGE_AFTER:  # in place: this rank's slice already sits at its offset
                 dist.all_gather_into_tensor(ys[n], ys[n][lo:hi])
 
     if world > 1 and not even:
@@ -572,6 +591,7 @@ def layer70b_leg(args, torch, lib, dev, rank, world):
     per_proj = {n: round(timed(step, n), 2) for n in layer} if world == 1 else None
     lib.mg_pdl_early_trigger(trigger_before)
     us, fused_note, max_diff = us_nccl, None, None
+    final_o = ys["o_proj"].clone()  # gathered o_proj output of the last weight copy
     if world > 1:
         # the same layer with the all-gather done by the matvec kernels themselves: every result row
         # is stored into all peers' arenas over NVLink, the kernel ends with the flag handshake
@@ -602,7 +622,7 @@ def layer70b_leg(args, torch, lib, dev, rank, world):
                     for site, (n, (w, lo, hi, bpr)) in enumerate(copies[c].items()):
                         if only is not None and n != only:
                             continue
-                        if lib.mg_peer_fuse_next(xh, site):
+                        if n in EXCHANGE_AFTER and lib.mg_peer_fuse_next(xh, site):
                             raise RuntimeError("mg_peer_fuse_next")
                         e2 = lib.launch_matvec_q4k_on_stream(w.data_ptr(), xs[n].data_ptr(), arena + offs[n] + 4 * lo,
                                                              hi - lo, bpr, s)
@@ -615,23 +635,50 @@ def layer70b_leg(args, torch, lib, dev, rank, world):
                     raise RuntimeError("peer exchange: a bounded wait expired")
                 # both paths end on the same weight copy: the gathered vectors must be identical
                 max_diff = 0.0
-                for n in names:
+                for n in EXCHANGE_AFTER:
                     got = torch.empty_like(ys[n])
                     lib.mg_memcpy_d2d(got.data_ptr(), arena + offs[n], 4 * layer[n][0])
                     torch.cuda.synchronize()
                     max_diff = max(max_diff, float((got - ys[n]).abs().max().item()))
+                    if n == "o_proj":
+                        final_o = got.clone()
             dist.barrier()
             lib.mg_peer_exchange_destroy(xh)
     total = sum(o * (i // 256) * 144 + 4 * i + 4 * o for o, i in layer.values())
     peak, kind = measured_peak()
-    gathered = sum(4 * o for o, i in layer.values()) if world > 1 else 0
+    gathered = sum(4 * layer[n][0] for n in EXCHANGE_AFTER) if world > 1 else 0
+    # the gathered o_proj vector against the CPU oracle: 48 sampled rows of every rank's shard
+    oracle_err = None
+    if rank == 0:
+        import oracle
+        oracle.build()
+        orc = oracle.lib()
+        o, i = layer["o_proj"]
+        y_host = final_o.cpu().numpy().astype(np.float64)
+        x_host = xs["o_proj"].cpu().numpy()
+        pidx = list(layer).index("o_proj")
+        got_rows, ref_rows = [], []
+        for r in range(world):
+            lo, hi = shard_rows(o, r, world)
+            wr = synth.q4k_matrix(hi - lo, i, np.random.Generator(np.random.PCG64([44, n_copies - 1, pidx, r])))
+            pick = np.unique(np.random.Generator(np.random.PCG64([46, r])).integers(0, hi - lo, 48))
+            sub = wr.reshape(hi - lo, -1)[pick].reshape(-1)
+            ref_rows.append(orc.matvec_f64(sub, x_host, pick.size, i // 256))
+            got_rows.append(y_host[lo + pick])
+        ref, got_v = np.concatenate(ref_rows), np.concatenate(got_rows)
+        oracle_err = float(np.max(np.abs(got_v - ref)) / np.sqrt(np.mean(ref * ref)))
     out = {"workload": "70B-class decoder layer (8192 / 28672, 64/8 heads), 7 Q4_K matvecs, batch 1",
            "n_gpus": world, "us_per_layer": round(us, 2), "gbs_total": round(total / us / 1e3, 1),
            "hbm_frac_per_gpu": round(total / us / 1e3 / world / peak, 4), "peak_source": f"of {kind}",
            "bytes_per_layer": total, "allgather_bytes_per_layer": gathered,
-           "collective": ("all-gather of the output slices fused into the 7 matvec kernels (peer stores over NVLink)"
-                          if world > 1 and fused_note is None else
-                          "7 NCCL all-gathers of the output slices per layer, inside the graph" if world > 1 else "none"),
+           "collective": ("4 all-gathers per layer, as the decode engine issues them (q/k stay rank-local under "
+                          "head-parallel attention; the exchanges follow v_proj - standing in for the attention "
+                          "output -, o_proj, up_proj - standing in for the SwiGLU slice - and down_proj), "
+                          + ("fused into the producing matvec kernels (peer stores over NVLink)"
+                             if fused_note is None else "NCCL all-gathers inside the graph")
+                          if world > 1 else "none"),
+           "oracle_check": {"projection": "o_proj", "rows": "48 sampled rows per shard", "max_err_over_rms": oracle_err,
+                            "bound": 1e-5, "ok": None if oracle_err is None else bool(oracle_err <= 1e-5)},
            "us_per_layer_nccl": round(us_nccl, 2) if world > 1 else None,
            "fused_vs_nccl_max_abs_diff": max_diff, "note": fused_note, "per_projection_us": per_proj,
            "weight_copies_rotated": n_copies, "launch": "CUDA graph replay"}
