@@ -246,6 +246,18 @@ int mg_rope_kv_append_f16_on_stream(float* q, float* k, const float* v, void* k_
                                     const int* pos_dev, int n_heads, int n_kv_heads, int head_dim, float base,
                                     const float* freq_table, void* stream);
 
+/* Both steps and the merge of the split results in ONE launch: q, k_new, v_new as the projections
+ * left them (f32, not rotated, not modified); k_new is rotated, both are rounded to half, appended
+ * at position pos (or *pos_dev) and used; the output is the attention over positions 0 .. pos
+ * (rocm_gemma.rs:429-489 issues rope, cache write and attention as separate launches).
+ * `scratch`: mg_sdpa_rope_f16kv_scratch_bytes(...) bytes, ZEROED ONCE by the caller after allocation
+ * (ticket counters that every launch leaves at zero).  n_splits <= 160. */
+size_t mg_sdpa_rope_f16kv_scratch_bytes(int n_heads, int n_kv_heads, int head_dim, int n_splits);
+int mg_sdpa_rope_decode_f16kv_on_stream(const float* q, const float* k_new, const float* v_new, void* k_cache,
+                                        void* v_cache, float* out, int n_heads, int n_kv_heads, int head_dim, int pos,
+                                        const int* pos_dev, float scale, float rope_base, const float* freq_table,
+                                        void* scratch, int n_splits, void* stream);
+
 /* Dense half pieces: y = W_half[out_dim][in_dim] . x (the dense-matrix arm of the reference
  * matvec, llm.rs:478-492; in_dim % 256 == 0, <= 12288), embedding row lookup (llm.rs:898-918)
  * and first-maximum arg-max where NaN never wins (rocm_gemma.rs:34-41; scratch: 2048 bytes). */

@@ -90,6 +90,8 @@ SIGNATURES = {
     "mg_sdpa_f16kv_scratch_bytes": (sz, [ci, ci, ci]),
     "mg_sdpa_decode_f16kv_on_stream": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, vp, cf, vp, ci, vp]),
     "mg_rope_kv_append_f16_on_stream": (ci, [vp, vp, vp, vp, vp, ci, vp, ci, ci, ci, cf, vp, vp]),
+    "mg_sdpa_rope_f16kv_scratch_bytes": (sz, [ci, ci, ci, ci]),
+    "mg_sdpa_rope_decode_f16kv_on_stream": (ci, [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, cf, cf, vp, vp, ci, vp]),
     "mg_matvec_f16_on_stream": (ci, [vp, vp, vp, ci, ci, vp]),
     "mg_embed_f16_on_stream": (ci, [vp, ci, vp, vp, ci, ci, vp]),
     "mg_argmax_on_stream": (ci, [vp, ci, vp, vp, vp, vp, vp]),

@@ -275,6 +275,252 @@ __global__ void rope_append_f16_kernel(float* q, float* k, const float* v,
     }
 }
 
+constexpr int kMaxSplitsOneLaunch = 160;  // one split per SM and KV head at most
+
+// ---- one launch per layer: RoPE + cache append + split attention + merge ---------------------------
+// q, k_new, v_new arrive as the projections left them (f32, not rotated).  Every CTA (KV head, split)
+// rotates the query heads of its group in registers; the CTA whose split holds the new position
+// rotates k_new, rounds it and v_new to half, appends both to the cache for the tokens to come and
+// uses the rounded values itself (the cache row it would otherwise read is the one it writes).
+// The per-split partials go to scratch as in the two-kernel form; the LAST CTA of a KV head to get
+// there (a ticket per KV head, counters zeroed once by the caller and left at zero by every
+// launch) merges the splits of the group's heads and writes the output, with the exchange of the
+// sharded engine where one is set.  Numerics are those of rope_append_f16_kernel followed by
+// sdpa_split_f16_kernel and sdpa_merge_kernel.
+template <int EPL, int GRP>
+__global__ void __launch_bounds__(256)
+sdpa_rope_split_f16_kernel(const float* q, const float* k_new, const float* v_new, __half* k_cache, __half* v_cache,
+                           float* partial, unsigned* counters, float* out, const int* pos_dev, int pos_arg,
+                           int n_kv_heads, int kv_dim, float scale, int n_splits, float rope_base,
+                           const float* freq_table, int hold_trigger, const mgpeer::PeerSync peer) {
+    mg::pdl_prologue(hold_trigger);
+    constexpr int HD = EPL * 32, HALF = HD / 2;
+    __shared__ float sh[8][GRP][HD + 2];
+    __shared__ float wsplit[GRP][kMaxSplitsOneLaunch];
+    __shared__ float lsum[GRP];
+    __shared__ int is_last;
+    const int kv_h = blockIdx.x, split = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = pos_dev ? *pos_dev : pos_arg;
+    const int seq_len = pos + 1;
+    const int chunk = (seq_len + n_splits - 1) / n_splits;
+    const int t0 = split * chunk, t1 = min(seq_len, t0 + chunk);
+    const bool has_new = pos >= t0 && pos < t1;   // then pos == t1 - 1
+    const int t_end = has_new ? t1 - 1 : t1;       // positions read from the cache
+
+    // rotation factors of this lane's dims (NEOX pairs: d and d +- HD/2 share a frequency)
+    float rc[EPL], rs[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+        const int i = (lane * EPL + e) % HALF;
+        // f64 pow rounded once: matches a correctly rounded powf (angles reach thousands of radians)
+        const float freq = freq_table ? freq_table[i] : (float)pow((double)rope_base, (double)(-2.0f * (float)i / (float)HD));
+        sincosf((float)pos * freq, &rs[e], &rc[e]);
+    }
+    auto rotate = [&](const float* vec, float (&dst)[EPL]) {
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+            const int d = lane * EPL + e;
+            if (d < HALF) {
+                const float x0 = vec[d], x1 = vec[d + HALF];
+                dst[e] = x0 * rc[e] - x1 * rs[e];
+            } else {
+                const float x0 = vec[d - HALF], x1 = vec[d];
+                dst[e] = x0 * rs[e] + x1 * rc[e];
+            }
+        }
+    };
+    float qr[GRP][EPL], o[GRP][EPL], m[GRP], l[GRP];
+#pragma unroll
+    for (int g = 0; g < GRP; ++g) {
+        rotate(q + (size_t)(kv_h * GRP + g) * HD, qr[g]);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) { qr[g][e] *= scale; o[g][e] = 0.0f; }
+        m[g] = -INFINITY;
+        l[g] = 0.0f;
+    }
+    float knew[EPL], vnew[EPL];
+    if (has_new && warp == 0) {
+        rotate(k_new + (size_t)kv_h * HD, knew);
+        __half kh[EPL], vh[EPL];
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+            kh[e] = __float2half_rn(knew[e]);
+            vh[e] = __float2half_rn(v_new[(size_t)kv_h * HD + lane * EPL + e]);
+            knew[e] = __half2float(kh[e]);
+            vnew[e] = __half2float(vh[e]);
+        }
+        const size_t off = (size_t)pos * kv_dim + (size_t)kv_h * HD + lane * EPL;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) { k_cache[off + e] = kh[e]; v_cache[off + e] = vh[e]; }
+    }
+    auto account = [&](const float (&kr)[EPL], const float (&vr)[EPL]) {
+#pragma unroll
+        for (int g = 0; g < GRP; ++g) {
+            float p = 0.0f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) p = fmaf(qr[g][e], kr[e], p);
+            const float sc = q4k::warp_sum(p);
+            const float m_new = fmaxf(m[g], sc);
+            const float a = expf(m[g] - m_new), b = expf(sc - m_new);
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) o[g][e] = fmaf(o[g][e], a, b * vr[e]);
+            l[g] = fmaf(l[g], a, b);
+            m[g] = m_new;
+        }
+    };
+    // Four positions per step: their K and V rows are all requested before any is used.
+    constexpr int kB = 4;
+    for (int tb = t0 + warp; tb < t_end; tb += 8 * kB) {
+        float kv[kB][EPL], vv[kB][EPL];
+#pragma unroll
+        for (int j = 0; j < kB; ++j) {
+            const int t = min(tb + 8 * j, t_end - 1);
+            load_half_row<EPL>(k_cache + (size_t)t * kv_dim + (size_t)kv_h * HD, lane, kv[j]);
+            load_half_row<EPL>(v_cache + (size_t)t * kv_dim + (size_t)kv_h * HD, lane, vv[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < kB; ++j) {
+            if (tb + 8 * j >= t_end) break;
+            account(kv[j], vv[j]);
+        }
+    }
+    if (has_new && warp == 0) account(knew, vnew);
+#pragma unroll
+    for (int g = 0; g < GRP; ++g) {
+        if (lane == 0) { sh[warp][g][0] = m[g]; sh[warp][g][1] = l[g]; }
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) sh[warp][g][2 + lane * EPL + e] = o[g][e];
+    }
+    __syncthreads();
+    // merge the 8 warps; thread -> (head g, dim d)
+    for (int idx = threadIdx.x; idx < GRP * HD; idx += blockDim.x) {
+        const int g = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) M = fmaxf(M, sh[w][g][0]);
+        float L = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const float mw = sh[w][g][0];
+            if (mw > -INFINITY) {
+                const float fw = expf(mw - M);
+                L = fmaf(sh[w][g][1], fw, L);
+                acc = fmaf(sh[w][g][2 + d], fw, acc);
+            }
+        }
+        float* dst = partial + ((size_t)(kv_h * GRP + g) * n_splits + split) * (HD + 2);
+        if (d == 0) { dst[0] = M; dst[1] = L; }
+        dst[2 + d] = acc;
+    }
+    // ---- the last CTA of this KV head merges the splits ---------------------------------------------------
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned ticket = atomicAdd(counters + kv_h, 1u);
+        is_last = ticket == (unsigned)n_splits - 1u;
+        if (is_last) counters[kv_h] = 0;  // every CTA of the head has taken its ticket: ready for the next launch
+    }
+    __syncthreads();
+    if (is_last) {
+        __threadfence();
+        const int stride = HD + 2;
+        // weights of the splits: warp g serves head g of the group (all heads at once)
+        for (int g = warp; g < GRP; g += 8) {
+            const float* pp = partial + (size_t)(kv_h * GRP + g) * n_splits * stride;
+            float mloc = -INFINITY;
+            for (int sidx = lane; sidx < n_splits; sidx += 32) {
+                const float ms = __ldcg(pp + (size_t)sidx * stride);
+                wsplit[g][sidx] = ms;
+                mloc = fmaxf(mloc, ms);
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, off));
+            float lloc = 0.0f;
+            for (int sidx = lane; sidx < n_splits; sidx += 32) {
+                const float ms = wsplit[g][sidx];
+                const float w = ms > -INFINITY ? expf(ms - mloc) : 0.0f;
+                wsplit[g][sidx] = w;
+                lloc = fmaf(__ldcg(pp + (size_t)sidx * stride + 1), w, lloc);
+            }
+            lloc = q4k::warp_sum(lloc);
+            if (lane == 0) lsum[g] = lloc;
+        }
+        __syncthreads();
+        // thread -> (head g, four consecutive dims): 8-byte loads (rows of HD + 2 floats are 8-byte
+        // aligned), four splits in flight
+        for (int idx = threadIdx.x; idx < GRP * (HD / 4); idx += blockDim.x) {
+            const int g = idx / (HD / 4), d = (idx % (HD / 4)) * 4;
+            const int h = kv_h * GRP + g;
+            const float* pp = partial + (size_t)h * n_splits * stride + 2 + d;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            int sidx = 0;
+            for (; sidx + 4 <= n_splits; sidx += 4) {
+                float2 lo[4], hi[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2* src = reinterpret_cast<const float2*>(pp + (size_t)(sidx + j) * stride);
+                    lo[j] = __ldcg(src);
+                    hi[j] = __ldcg(src + 1);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float w = wsplit[g][sidx + j];
+                    acc[0] = fmaf(lo[j].x, w, acc[0]); acc[1] = fmaf(lo[j].y, w, acc[1]);
+                    acc[2] = fmaf(hi[j].x, w, acc[2]); acc[3] = fmaf(hi[j].y, w, acc[3]);
+                }
+            }
+            for (; sidx < n_splits; ++sidx) {
+                const float2* src = reinterpret_cast<const float2*>(pp + (size_t)sidx * stride);
+                const float2 lo = __ldcg(src), hi = __ldcg(src + 1);
+                const float w = wsplit[g][sidx];
+                acc[0] = fmaf(lo.x, w, acc[0]); acc[1] = fmaf(lo.y, w, acc[1]);
+                acc[2] = fmaf(hi.x, w, acc[2]); acc[3] = fmaf(hi.y, w, acc[3]);
+            }
+            const float inv_den = lsum[g];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float r = acc[e] / inv_den;
+                const size_t o_idx = (size_t)h * HD + d + e;
+                if (peer.world > 1 && peer.stamp_slots != nullptr) {
+                    out[o_idx] = r;
+                    mgpeer::store_stamped_all(peer, (long long)o_idx, __float_as_uint(r),
+                                              mgpeer::exchange_epoch(peer.epoch_dev, peer.epoch_mul, peer.epoch_add));
+                } else if (peer.world > 1) mgpeer::store_all(peer, out + o_idx, r);
+                else out[o_idx] = r;
+            }
+        }
+    }
+    mgpeer::peer_finish(peer);  // all-gather of the heads: the grid ends when every rank's heads are here
+}
+
+template <int EPL>
+cudaError_t launch_rope_split(int grp, dim3 grid, cudaStream_t s, const float* q, const float* k_new, const float* v_new,
+                              __half* k, __half* v, float* partial, unsigned* counters, float* out, const int* pos_dev,
+                              int pos, int n_kv_heads, int kv_dim, float scale, int n_splits, float base,
+                              const float* freq_table, int hold, const mgpeer::PeerSync& peer) {
+#define MG_RSPLIT_CASE(G)                                                                                       \
+    case G:                                                                                                     \
+        return mg::launch_pdl(sdpa_rope_split_f16_kernel<EPL, G>, grid, dim3(256), 0, s, q, k_new, v_new, k, v, \
+                              partial, counters, out, pos_dev, pos, n_kv_heads, kv_dim, scale, n_splits, base,  \
+                              freq_table, hold, peer);
+    // (head_dim 256 with groups of 7 or 8 would exceed the static shared-memory limit)
+    if (EPL == 8 && grp > 4) return cudaErrorInvalidValue;
+    switch (grp) {
+        MG_RSPLIT_CASE(1) MG_RSPLIT_CASE(2) MG_RSPLIT_CASE(3) MG_RSPLIT_CASE(4)
+        default:
+            if constexpr (EPL < 8) {
+                switch (grp) {
+                    MG_RSPLIT_CASE(7) MG_RSPLIT_CASE(8)
+                    default: return cudaErrorInvalidValue;
+                }
+            } else {
+                return cudaErrorInvalidValue;
+            }
+    }
+#undef MG_RSPLIT_CASE
+}
+
 template <int EPL>
 cudaError_t launch_split(int grp, dim3 grid, cudaStream_t s, const float* q, const __half* k, const __half* v,
                          float* partial, const int* seq_dev, int seq_len, int n_kv_heads, int kv_dim,
@@ -367,6 +613,48 @@ int mg_sdpa_decode_f16kv_on_stream(const float* q, const void* k_cache, const vo
     if (e != cudaSuccess) return (int)e;
     return (int)mg::launch_pdl(sdpa_merge_kernel, dim3((unsigned)n_heads), dim3(128), 0, s, (const float*)part, out,
                                head_dim, n_splits, mg::early_trigger_flag() ? 0 : 1, peer);
+}
+
+// Scratch of the one-launch form below: the per-split partials, then one ticket counter per KV
+// head.  The caller zeroes the scratch ONCE after allocating it; every launch leaves the counters at zero.
+size_t mg_sdpa_rope_f16kv_scratch_bytes(int n_heads, int n_kv_heads, int head_dim, int n_splits) {
+    if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || n_splits <= 0) return 0;
+    const size_t part = ((size_t)n_heads * n_splits * (head_dim + 2) * sizeof(float) + 255) & ~(size_t)255;
+    return part + (((size_t)n_kv_heads * sizeof(unsigned) + 255) & ~(size_t)255);
+}
+
+// RoPE (NEOX pairs, position *pos_dev or pos) of q and k_new, k_new / v_new appended to the half
+// cache at that position, attention of every query head over positions 0 .. pos, in ONE launch;
+// the counterpart of rope -> cache write -> attention in RocmGemma::attention_layer
+// (crates/modgrad-gemma/src/rocm_gemma.rs:429-489).  q, k_new, v_new are not modified.
+int mg_sdpa_rope_decode_f16kv_on_stream(const float* q, const float* k_new, const float* v_new, void* k_cache,
+                                        void* v_cache, float* out, int n_heads, int n_kv_heads, int head_dim, int pos,
+                                        const int* pos_dev, float scale, float rope_base, const float* freq_table,
+                                        void* scratch, int n_splits, void* stream) {
+    const mgpeer::PeerSync peer = mgpeer::take_next_peer_sync();  // consumed on every path, errors included
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_splits <= 0 || n_splits > kMaxSplitsOneLaunch)
+        return (int)cudaErrorInvalidValue;
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return (int)cudaErrorInvalidValue;
+    if (!pos_dev && pos < 0) return (int)cudaErrorInvalidValue;
+    if (!q || !k_new || !v_new || !k_cache || !v_cache || !out || !scratch) return (int)cudaErrorInvalidValue;
+    if (peer.world > 1 && !mgpeer::in_arena(peer, out, (size_t)n_heads * head_dim * sizeof(float))) return (int)cudaErrorInvalidValue;
+    const int grp = n_heads / n_kv_heads, kv_dim = n_kv_heads * head_dim;
+    const dim3 grid((unsigned)n_kv_heads, (unsigned)n_splits);
+    cudaStream_t s = (cudaStream_t)stream;
+    __half* k = static_cast<__half*>(k_cache);
+    __half* v = static_cast<__half*>(v_cache);
+    float* part = static_cast<float*>(scratch);
+    const size_t part_bytes = ((size_t)n_heads * n_splits * (head_dim + 2) * sizeof(float) + 255) & ~(size_t)255;
+    unsigned* counters = reinterpret_cast<unsigned*>(static_cast<unsigned char*>(scratch) + part_bytes);
+    const int hold = mg::early_trigger_flag() ? 0 : 1;
+    if (head_dim == 128)
+        return (int)launch_rope_split<4>(grp, grid, s, q, k_new, v_new, k, v, part, counters, out, pos_dev, pos, n_kv_heads,
+                                         kv_dim, scale, n_splits, rope_base, freq_table, hold, peer);
+    if (head_dim == 256)
+        return (int)launch_rope_split<8>(grp, grid, s, q, k_new, v_new, k, v, part, counters, out, pos_dev, pos, n_kv_heads,
+                                         kv_dim, scale, n_splits, rope_base, freq_table, hold, peer);
+    return (int)launch_rope_split<2>(grp, grid, s, q, k_new, v_new, k, v, part, counters, out, pos_dev, pos, n_kv_heads,
+                                     kv_dim, scale, n_splits, rope_base, freq_table, hold, peer);
 }
 
 // freq_table (device, head_dim/2 floats, may be null): base^(-2i/head_dim) precomputed by the

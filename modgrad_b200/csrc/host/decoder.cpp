@@ -274,7 +274,6 @@ int queue_token_impl(mg_decoder* d) {
     const float scale = 1.0f / sqrtf((float)hd);
     int e;
     int* pos_dev = d->state;
-    int* seq_dev = d->state + 1;
     int* step_dev = d->state + 2;
     int* tok_dev = d->state + 3;
 
@@ -291,16 +290,15 @@ int queue_token_impl(mg_decoder* d) {
                                                            D / 256, s)))
                 return fail(d, e, "qkv");
         }
-        if ((e = mg_rope_kv_append_f16_on_stream(d->q, d->k, d->v, L.k_cache, L.v_cache, 0, pos_dev, Hl, KVl, hd,
-                                                 c.rope_base, d->rope_freq, s)))
-            return fail(d, e, "rope");
-        // this rank's heads land at their place in the full attention vector (and, fused, in
-        // every peer's: the merge kernel ends with the exchange)
+        // RoPE, cache append, attention and the merge of its splits in one launch.  This rank's heads land
+        // at their place in the full attention vector (and, fused, in every peer's: the kernel ends with
+        // the exchange).
         if (d->stamped) mgpeer::set_next_peer_sync(stamp_out(d, kSiteHeads, d->s_att, (long long)d->h0 * hd, l));
         else if (d->fused) mgpeer::set_next_peer_sync(mgpeer::make_sync(d->px, kSiteHeads));
-        if ((e = mg_sdpa_decode_f16kv_on_stream(d->q, L.k_cache, L.v_cache, d->att_full + (size_t)d->h0 * hd, Hl, KVl,
-                                                hd, 0, seq_dev, scale, d->attn_scratch, d->n_splits, s)))
-            return fail(d, e, "sdpa");
+        if ((e = mg_sdpa_rope_decode_f16kv_on_stream(d->q, d->k, d->v, L.k_cache, L.v_cache, d->att_full + (size_t)d->h0 * hd,
+                                                     Hl, KVl, hd, 0, pos_dev, scale, c.rope_base, d->rope_freq,
+                                                     d->attn_scratch, d->n_splits, s)))
+            return fail(d, e, "attention");
         if (!d->fused && (e = gather_heads(d))) return e;
         {   // hidden += Wo . att.  One GPU: in place.  Fused: this rank's rows are added in place and
             // stored into every rank's hidden state by the matvec itself.  Otherwise the rows are
@@ -618,9 +616,13 @@ int mg_decoder_create_sharded(const mg_decoder_config* cfg, int rank, int world,
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int kv_n = d->kv1 - d->kv0;
-    d->n_splits = sms / kv_n > 0 ? sms / kv_n : 1;
-    if ((rc = dev_alloc(d, &tmp, mg_sdpa_f16kv_scratch_bytes(d->h1 - d->h0, hd, d->n_splits)))) return bail(rc);
-    d->attn_scratch = tmp;
+    d->n_splits = sms / kv_n > 0 ? (sms / kv_n < 160 ? sms / kv_n : 160) : 1;  // the one-launch attention takes up to 160
+    {
+        const size_t nb = mg_sdpa_rope_f16kv_scratch_bytes(d->h1 - d->h0, kv_n, hd, d->n_splits);
+        if ((rc = dev_alloc(d, &tmp, nb))) return bail(rc);
+        if ((e = cudaMemset(tmp, 0, nb)) != cudaSuccess) return bail((int)e);  // the ticket counters start at zero
+        d->attn_scratch = tmp;
+    }
     if ((rc = dev_alloc(d, &tmp, (size_t)2 * 256 * 4 + 64))) return bail(rc);
     d->argmax_scratch = tmp;
     if ((rc = dev_alloc(d, &d->state, (size_t)8))) return bail(rc);
@@ -831,10 +833,11 @@ void* mg_decoder_weight_ptr(mg_decoder* d, int layer, int which) {
 }
 int mg_decoder_kernels_per_token(const mg_decoder* d) {
     if (!d) return 0;
-    if (d->world == 1) return 1 + d->cfg.n_layers * 8 + 5;
+    // per layer: qkv, attention (RoPE + append + splits + merge), o, gate/up, SwiGLU, down
+    if (d->world == 1) return 1 + d->cfg.n_layers * 6 + 5;
     // sharded: + the pair kernels at the end; + two residual adds per layer unless the matvecs
     // add in place (fused); + one gather kernel per collective in the peer-kernel mode
-    int n = 1 + d->cfg.n_layers * (d->fused ? 8 : 10) + 7;
+    int n = 1 + d->cfg.n_layers * (d->fused ? 6 : 8) + 7;
     if (d->peer && !d->fused) n += 4 * d->cfg.n_layers + 1;
     return n;
 }

@@ -136,6 +136,47 @@ def test_attention_half_cache_split(orc, cuda, n_heads, n_kv, hd, seq):
         assert rel_rms_err(down(od, q.size), want) < 1e-5, splits
 
 
+@pytest.mark.parametrize("n_heads,n_kv,hd,pos", [(28, 4, 128, 2303), (4, 2, 128, 0), (4, 2, 128, 16), (8, 8, 64, 199),
+                                                 (4, 1, 256, 89), (7, 1, 128, 5)])
+def test_attention_one_launch_matches_rope_append_then_split(cuda, n_heads, n_kv, hd, pos):
+    """RoPE + cache append + attention + merge in one launch against the separate launches
+    (which the tests above and the rope test pin to the oracle): same output, same cache rows,
+    inputs untouched, ticket counters back at zero (a second launch gives the same result)."""
+    rng = np.random.Generator(np.random.PCG64(pos + n_heads))
+    kv_dim, seq = n_kv * hd, pos + 1
+    q = rng.standard_normal(n_heads * hd, dtype=np.float32)
+    kn = rng.standard_normal(kv_dim, dtype=np.float32)
+    vn = rng.standard_normal(kv_dim, dtype=np.float32)
+    k = rng.standard_normal(seq * kv_dim, dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal(seq * kv_dim, dtype=np.float32).astype(np.float16)
+    scale, base = 1.0 / np.sqrt(hd), 1e6
+    # separate launches
+    q1, k1, v1, kc1, vc1, o1 = up(q), up(kn), up(vn), up(k), up(v), DeviceBuffer(q.nbytes)
+    assert cuda.mg_rope_kv_append_f16_on_stream(q1.ptr, k1.ptr, v1.ptr, kc1.ptr, vc1.ptr, pos, None, n_heads, n_kv, hd,
+                                                base, None, None) == 0
+    sc1 = DeviceBuffer(cuda.mg_sdpa_f16kv_scratch_bytes(n_heads, hd, 7))
+    assert cuda.mg_sdpa_decode_f16kv_on_stream(q1.ptr, kc1.ptr, vc1.ptr, o1.ptr, n_heads, n_kv, hd, seq, None, scale,
+                                               sc1.ptr, 7, None) == 0
+    kern.sync()
+    want = down(o1, q.size)
+    want_k = kc1.copy_to_host_bytes(np.empty_like(k))
+    want_v = vc1.copy_to_host_bytes(np.empty_like(v))
+    for splits in (1, 7, 37):
+        q2, k2, v2, kc2, vc2, o2 = up(q), up(kn), up(vn), up(k), up(v), DeviceBuffer(q.nbytes)
+        nb = cuda.mg_sdpa_rope_f16kv_scratch_bytes(n_heads, n_kv, hd, splits)
+        sc2 = DeviceBuffer(nb)
+        sc2.copy_from_host_bytes(np.zeros(nb, dtype=np.uint8))
+        for rep in range(2):
+            assert cuda.mg_sdpa_rope_decode_f16kv_on_stream(q2.ptr, k2.ptr, v2.ptr, kc2.ptr, vc2.ptr, o2.ptr, n_heads, n_kv,
+                                                            hd, pos, None, scale, base, None, sc2.ptr, splits, None) == 0
+            kern.sync()
+            got = down(o2, q.size)
+            assert rel_rms_err(got, want) < 2e-6, (splits, rep)
+        assert np.array_equal(kc2.copy_to_host_bytes(np.empty_like(k)).view(np.uint16), want_k.view(np.uint16))
+        assert np.array_equal(vc2.copy_to_host_bytes(np.empty_like(v)).view(np.uint16), want_v.view(np.uint16))
+        assert np.array_equal(down(q2, q.size), q) and np.array_equal(down(k2, kn.size), kn)
+
+
 def test_attention_f32_cache_reference_launchers(cuda):
     rng = np.random.Generator(np.random.PCG64(8))
     n_heads, n_kv, hd, seq = 8, 2, 96, 77
