@@ -397,6 +397,10 @@ def main():
     del copies, xs, ys
     torch.cuda.empty_cache()
     layer70b = None if args.no_layer70b else layer70b_leg(args, torch, lib, dev, rank, world)
+    if layer70b is not None and "skipped" not in layer70b:
+        eng = layer70b_engine_leg(args, rank, world)
+        if rank == 0:
+            layer70b["engine"] = eng
     if world > 1 and not args.no_decode:
         decode_sharded = decode_leg_sharded(args, rank, world)
     if rank == 0:
@@ -685,6 +689,51 @@ def layer70b_leg(args, torch, lib, dev, rank, world):
     del copies
     torch.cuda.empty_cache()
     return out
+
+
+def layer70b_engine_leg(args, rank, world):
+    """The same 70B-class layer as the decode ENGINE runs it (grouped q/k/v and gate/up launches with the
+    RMSNorm in front, one-launch attention over a short context, SwiGLU into limb records, the four
+    exchanges per layer in the engine's default protocol): two random-init engines of 2 and 6 layers
+    decode the same tokens; the difference of their times per token is four layers."""
+    import torch
+    import torch.distributed as dist
+    from modgrad_b200 import decoder as dec, shard
+    prefill, tokens = 64, 48
+    ms_tok, mode, kpt = {}, None, {}
+    for n_layers in (2, 6):
+        cfg = dec.DecoderConfig(n_layers=n_layers, d_model=8192, n_heads=64, n_kv_heads=8, head_dim=128, d_ff=28672,
+                                vocab=32768, max_seq=prefill + tokens + 16, rms_eps=1e-5, rope_base=5e5)
+        nccl_id = shard.nccl_id_from_torch(rank) if world > 1 else None
+        d = dec.Q4KDecoder(cfg, rank, world, nccl_id)
+        d.load_random_shard(7, prefill=prefill)
+        if world > 1:
+            dist.barrier()
+        d.generate(1, 4)
+        d.set_position(prefill)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        _, ms = d.generate(1, tokens)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        ms_tok[n_layers] = ms / tokens
+        kpt[n_layers] = d.kernels_per_token()
+        mode = d.gather_mode() if world > 1 else "none"
+        d.close()
+        del d
+        torch.cuda.empty_cache()
+    us_layer = (ms_tok[6] - ms_tok[2]) * 1e3 / 4
+    layer_bytes70 = sum(o * (i // 256) * 144 for o, i in synth.LLAMA_70B_LAYER.values())
+    peak, kind = measured_peak()
+    return {"us_per_layer": round(us_layer, 2), "gbs_total": round(layer_bytes70 / us_layer / 1e3, 1),
+            "hbm_frac_per_gpu": round(layer_bytes70 / us_layer / 1e3 / world / peak, 4), "peak_source": f"of {kind}",
+            "ms_per_token_2_layers": round(ms_tok[2], 4), "ms_per_token_6_layers": round(ms_tok[6], 4),
+            "kernels_per_layer": (kpt[6] - kpt[2]) // 4, "exchange": mode, "exchanges_per_layer": 4 if world > 1 else 0,
+            "context": f"{prefill} prefilled + {tokens} decoded positions",
+            "method": "time per token of a 6-layer engine minus that of a 2-layer engine, over 4"}
 
 
 def decode_leg_sharded(args, rank, world):
