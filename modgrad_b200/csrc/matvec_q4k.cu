@@ -517,10 +517,7 @@ extern "C" int mg_matvec_q4k_bias_on_stream(const uint8_t* w_q4, const float* x,
     // Matrices of many short rows go to the tensor-core kernel (half an SM per CTA, speculative
     // start: consecutive launches overlap); few rows or long rows are faster on the dp4a ring
     // kernel below, whose x conversion is lighter.
-    static const int force_mma = [] { const char* e = getenv("MODGRAD_Q4K_GEMV_MMA"); return e ? atoi(e) : -1; }();
-    const bool want_mma = force_mma >= 0 ? force_mma != 0
-                                         : (out_dim >= kMmaMinRows && gemvmma::fits_half_sm(blocks_per_row)) ||
-                                               !limbs_path_ok(blocks_per_row);
+    const bool want_mma = (out_dim >= kMmaMinRows && gemvmma::fits_half_sm(blocks_per_row)) || !limbs_path_ok(blocks_per_row);
     if (peer.world <= 1 && want_mma && gemvmma::supported(blocks_per_row)) {
         // the tensor-core kernel: one launch, x converted inside, no scratch
         const mg::DeviceProps& dp = mg::device_props();
