@@ -182,9 +182,10 @@ int mg_swiglu_limbs_on_stream(const float* gate, const float* up, float* act_out
 /* ---- multi-sequence dequant-GEMM on the tensor cores (tcgen05 + TMEM), M <= 64 per call --------
  * Y[m][out_dim] = X[m][K] . dequant(W)^T: the batched contract of Linear::forward_batched
  * (crates/modgrad-device/src/backend/tensor.rs:1839-1853) for Q4_K weights; no reference kernel
- * exists for it (compared with M independent CPU matvecs).  X is f32 [m_rows][K] and is taken
- * in HALF precision by contract (each row scaled by a power of two so that its largest
- * magnitude lies in [2^9, 2^10), rounded once to IEEE half, scaled back exactly); y must hold round-up(m_rows to 16/32/64) * out_dim floats;
+ * exists for it (compared with M independent CPU matvecs on the same f32 X, 1e-5 of the output
+ * rms).  X is f32 [m_rows][K]; each row is carried as two half-precision limbs after a power-of-two
+ * scale (22 significant bits relative to the row's largest magnitude).  Exactly m_rows * out_dim
+ * floats of y are written.
  * `scratch`: mg_matmul_q4k_scratch_bytes(m_rows, blocks_per_row) bytes of device memory,
  * 1024-byte aligned.  mg_matmul_q4k_status (after a synchronise) returns 702 if a bounded
  * wait inside the kernel expired, else 0. */

@@ -28,6 +28,12 @@ __device__ __forceinline__ void griddep_launch_dependents() {
 // ---------------------------------------------------------------------------------------------
 // Converts activations 4*chunk .. 4*chunk+3 (v) and writes this thread's share of the record
 // of their sub-block; the 8 threads of a sub-block (8 consecutive lanes) call it together.
+// PEER selects the exchange code that is compiled in: 0 none, 1 plain peer stores + handshake,
+// 2 stamped words (peer_sync.cuh).  Kernels carry only the form they use: their code size decides
+// how well the instruction cache serves the hot loop (the single-GPU GEMV lost 20 % when all of it
+// was compiled into one kernel).
+constexpr int kPeerNone = 0, kPeerFused = 1, kPeerStamped = 2;
+template <int PEER = kPeerNone>
 __device__ __forceinline__ void convert_chunk(const float (&v)[4], int chunk, uint32_t* __restrict__ rec,
                                               bool store = true, const mgpeer::PeerSync* peer = nullptr) {
     const int sub = chunk >> 3, t = chunk & 7;
@@ -66,7 +72,7 @@ __device__ __forceinline__ void convert_chunk(const float (&v)[4], int chunk, ui
     // A non-finite activation poisons its sub-block: the scale becomes NaN, so every
     // row's sum becomes NaN as it does in the reference (w * NaN).
     const float sc = bad ? __uint_as_float(0x7FC00000u) : s;
-    if (peer != nullptr && peer->world > 1 && peer->stamp_slots != nullptr) {
+    if (PEER == kPeerStamped && peer != nullptr && peer->world > 1 && peer->stamp_slots != nullptr) {
         // records all-gathered word by word, every word stamped with the exchange's epoch
         const unsigned epoch = mgpeer::exchange_epoch(peer->epoch_dev, peer->epoch_mul, peer->epoch_add);
         const long long w0 = plane - rec, r0 = r - rec;  // word offsets inside this rank's record slice
@@ -79,7 +85,7 @@ __device__ __forceinline__ void convert_chunk(const float (&v)[4], int chunk, ui
         }
         return;
     }
-    if (peer != nullptr && peer->world > 1) {  // records all-gathered by the producing kernel
+    if (PEER == kPeerFused && peer != nullptr && peer->world > 1) {  // records all-gathered by the producing kernel
         mgpeer::store_all(*peer, plane + t, l2);
         mgpeer::store_all(*peer, plane + 8 + t, l1);
         mgpeer::store_all(*peer, plane + 16 + t, l0);
@@ -300,7 +306,7 @@ __device__ __forceinline__ void compute_window(const Window<R>& wd, const uint4*
 // Fills the CTA's shared-memory record table: from the f32 activation vector (FROM_X = 1,
 // optional RMSNorm in front; bpr <= 32 so four chunks per thread cover the vector in one pass)
 // or by copying records made by x_to_limbs_kernel (FROM_X = 0).  Ends with __syncthreads().
-template <int FROM_X, bool COHERENT>
+template <int FROM_X, bool COHERENT, int PEER>
 __device__ __forceinline__ void stage_records(const MatList& ml, const void* src, int x_aligned, int bpr,
                                               uint4* rec_s) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -315,7 +321,7 @@ __device__ __forceinline__ void stage_records(const MatList& ml, const void* src
         for (int u = 0; u < kU; ++u) {
             const int c = threadIdx.x + u * kGemvThreads;
             if (c < n_chunks) {
-                if (ml.xin.slots != nullptr)
+                if (PEER == kPeerStamped && ml.xin.slots != nullptr)
                     load_chunk_stamped(v[u], ml.xin, c, mgpeer::exchange_epoch(ml.xin.epoch_dev, ml.xin.epoch_mul, ml.xin.epoch_add));
                 else
                     load_chunk<COHERENT>(v[u], x, c, x_aligned);
@@ -361,7 +367,7 @@ __device__ __forceinline__ void stage_records(const MatList& ml, const void* src
     } else {
         const uint4* rec_g = static_cast<const uint4*>(src);
         const int n_vec = bpr * 4 * xlimbs::kRecordVec4;
-        if (ml.xin.slots != nullptr) {  // stamped records: one slot per record word
+        if (PEER == kPeerStamped && ml.xin.slots != nullptr) {  // stamped records: one slot per record word
             const unsigned epoch = mgpeer::exchange_epoch(ml.xin.epoch_dev, ml.xin.epoch_mul, ml.xin.epoch_add);
             for (int i = threadIdx.x; i < n_vec; i += kGemvThreads) {
                 uint4 w;
@@ -386,7 +392,7 @@ __device__ __forceinline__ void stage_records(const MatList& ml, const void* src
 // (persistent decode kernel): they are read with L2-level loads.  PDL = true: stand-alone
 // kernel chained with programmatic dependent launch.  block_id / n_blocks replace blockIdx /
 // gridDim so that a persistent kernel can run the body as one of its phases.
-template <int R, int FROM_X, bool COHERENT, bool PDL>
+template <int R, int FROM_X, bool COHERENT, bool PDL, int PEER>
 __device__ __forceinline__ void gemv_body(const MatList& ml, const void* src, int x_aligned, int bpr,
                                           int block_id, int n_blocks) {
     extern __shared__ __align__(16) uint4 rec_s[];  // the kernel's dynamic shared memory
@@ -415,7 +421,7 @@ __device__ __forceinline__ void gemv_body(const MatList& ml, const void* src, in
     }
 
     if (PDL) griddep_wait();  // x / the records may be produced by the kernel launched just before this one
-    stage_records<FROM_X, COHERENT>(ml, src, x_aligned, bpr, rec_s);
+    stage_records<FROM_X, COHERENT, PEER>(ml, src, x_aligned, bpr, rec_s);
 
     float acc[R];
 #pragma unroll
@@ -434,11 +440,11 @@ __device__ __forceinline__ void gemv_body(const MatList& ml, const void* src, in
                 const float s = q4k::warp_sum(acc[r]);
                 if (lane == 0 && row0 + r < rows) {
                     const float v = add ? s + ld_f32<COHERENT>(add + row0 + r) : s;
-                    if (ml.peer.world > 1 && ml.peer.stamp_slots != nullptr) {
+                    if (PEER == kPeerStamped && ml.peer.world > 1 && ml.peer.stamp_slots != nullptr) {
                         y[row0 + r] = v;
                         mgpeer::store_stamped_all(ml.peer, row0 + r, __float_as_uint(v),
                                                   mgpeer::exchange_epoch(ml.peer.epoch_dev, ml.peer.epoch_mul, ml.peer.epoch_add));
-                    } else if (ml.peer.world > 1) mgpeer::store_all(ml.peer, y + row0 + r, v);
+                    } else if (PEER == kPeerFused && ml.peer.world > 1) mgpeer::store_all(ml.peer, y + row0 + r, v);
                     else y[row0 + r] = v;
                 }
                 acc[r] = 0.0f;
@@ -522,7 +528,7 @@ __device__ __forceinline__ void load_window_smem(Window<R>& wd, const uint8_t* s
 
 // Dynamic shared memory: the record table, then kGemvWarps * depth stages.  `timeouts` counts
 // warps that gave up waiting for a stage (their rows are then left unwritten).
-template <int R, int FROM_X>
+template <int R, int FROM_X, int PEER>
 __device__ __forceinline__ void gemv_ring_body(const MatList& ml, const void* src, int x_aligned, int bpr,
                                                int depth, unsigned* timeouts) {
     extern __shared__ __align__(16) uint4 rec_s[];
@@ -588,7 +594,7 @@ __device__ __forceinline__ void gemv_ring_body(const MatList& ml, const void* sr
     }
 
     griddep_wait();  // x / the records may be produced by the kernel launched just before this one
-    stage_records<FROM_X, false>(ml, src, x_aligned, bpr, rec_s);
+    stage_records<FROM_X, false, PEER>(ml, src, x_aligned, bpr, rec_s);
 
     float acc[R];
 #pragma unroll
@@ -629,11 +635,11 @@ __device__ __forceinline__ void gemv_ring_body(const MatList& ml, const void* sr
                 const float s = q4k::warp_sum(acc[r]);
                 if (lane == 0 && cons.row0 + r < rows) {
                     const float v = add ? s + add[cons.row0 + r] : s;
-                    if (ml.peer.world > 1 && ml.peer.stamp_slots != nullptr) {
+                    if (PEER == kPeerStamped && ml.peer.world > 1 && ml.peer.stamp_slots != nullptr) {
                         y[cons.row0 + r] = v;
                         mgpeer::store_stamped_all(ml.peer, cons.row0 + r, __float_as_uint(v),
                                                   mgpeer::exchange_epoch(ml.peer.epoch_dev, ml.peer.epoch_mul, ml.peer.epoch_add));
-                    } else if (ml.peer.world > 1) mgpeer::store_all(ml.peer, y + cons.row0 + r, v);
+                    } else if (PEER == kPeerFused && ml.peer.world > 1) mgpeer::store_all(ml.peer, y + cons.row0 + r, v);
                     else y[cons.row0 + r] = v;
                 }
                 acc[r] = 0.0f;
@@ -645,7 +651,7 @@ __device__ __forceinline__ void gemv_ring_body(const MatList& ml, const void* sr
             parity ^= 1u;
         }
     }
-    mgpeer::peer_finish(ml.peer);
+    if (PEER == kPeerFused) mgpeer::peer_finish(ml.peer);
 }
 
 }  // namespace gemvdev

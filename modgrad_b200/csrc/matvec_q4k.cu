@@ -49,6 +49,7 @@ using namespace gemvdev;
 // up == nullptr: records of x.  up != nullptr: records of silu(x) * up, the SwiGLU product
 // (exact logistic, crates/modgrad-device/src/kfd/llm.rs:1065-1069), also stored as f32 to
 // `act_out` when that is given.
+template <int PEER>
 __global__ void __launch_bounds__(256) x_to_limbs_kernel(const float* x,
                                                          const float* up, float* act_out,
                                                          uint32_t* rec, int n_chunks,
@@ -77,17 +78,17 @@ __global__ void __launch_bounds__(256) x_to_limbs_kernel(const float* x,
             for (int i = 0; i < 4; ++i) act_out[(size_t)chunk * 4 + i] = v[i];
         }
     }
-    convert_chunk(v, chunk, rec, valid, &peer);
-    mgpeer::peer_finish(peer);
+    convert_chunk<PEER>(v, chunk, rec, valid, &peer);
+    if (PEER == kPeerFused) mgpeer::peer_finish(peer);
 }
 
 // FROM_X = 1: `src` is the f32 activation vector and every CTA converts it into its
 // shared-memory record table itself (one kernel per matvec); FROM_X = 0: `src` is a record
 // table in global memory made by x_to_limbs_kernel (several matvecs share one conversion).
-template <int R, int FROM_X>
+template <int R, int FROM_X, int PEER>
 __global__ void __launch_bounds__(kGemvThreads, 1)
 matvec_q4k_dp4a_kernel(const MatList ml, const void* src, int x_aligned, int bpr) {
-    gemv_body<R, FROM_X, false, true>(ml, src, x_aligned, bpr, (int)blockIdx.x, (int)gridDim.x);
+    gemv_body<R, FROM_X, false, true, PEER>(ml, src, x_aligned, bpr, (int)blockIdx.x, (int)gridDim.x);
 }
 
 // Warps of the ring kernel that gave up waiting for a bulk copy (never expected; a non-zero
@@ -96,10 +97,12 @@ __device__ unsigned g_ring_timeouts = 0;
 
 // The same arithmetic with the weight stream staged in shared memory by bulk asynchronous
 // copies (gemv_ring_body): the default path.
-template <int R, int FROM_X>
+// PEER (gemv_q4k_device.cuh): which exchange the launch ends with / reads its input from; the
+// instantiation for none carries none of that code.
+template <int R, int FROM_X, int PEER>
 __global__ void __launch_bounds__(kGemvThreads, 1)
 matvec_q4k_ring_kernel(const MatList ml, const void* src, int x_aligned, int bpr, int depth) {
-    gemv_ring_body<R, FROM_X>(ml, src, x_aligned, bpr, depth, &g_ring_timeouts);
+    gemv_ring_body<R, FROM_X, PEER>(ml, src, x_aligned, bpr, depth, &g_ring_timeouts);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -223,14 +226,14 @@ cudaError_t launch_f32(const uint8_t* w, const float* x, const float* bias, floa
 // ---------------------------------------------------------------------------------------------
 constexpr int kMaxRecordSmem = 200 * 1024;  // limb-record table limit: bpr <= 246
 
-template <int R, int FROM_X>
+template <int R, int FROM_X, int PEER>
 cudaError_t launch_dp4a(const MatList& ml, const void* src, int bpr, int sms, cudaStream_t stream) {
     const size_t smem = xlimbs::record_bytes((size_t)bpr * 256);
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(matvec_q4k_dp4a_kernel<R, FROM_X>,
+        cudaError_t e = cudaFuncSetAttribute(matvec_q4k_dp4a_kernel<R, FROM_X, PEER>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxRecordSmem);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
@@ -249,7 +252,7 @@ cudaError_t launch_dp4a(const MatList& ml, const void* src, int bpr, int sms, cu
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const int x_aligned = mg::aligned16(src) ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, matvec_q4k_dp4a_kernel<R, FROM_X>, ml, src, x_aligned, bpr);
+    return cudaLaunchKernelEx(&cfg, matvec_q4k_dp4a_kernel<R, FROM_X, PEER>, ml, src, x_aligned, bpr);
 }
 
 // Stages per warp the ring kernel can have for rows of `bpr` super-blocks at R rows per stage
@@ -261,14 +264,14 @@ int ring_depth(int bpr, int rows) {
     return d > kRingMaxDepth ? kRingMaxDepth : (d < 0 ? 0 : d);
 }
 
-template <int R, int FROM_X>
+template <int R, int FROM_X, int PEER>
 cudaError_t launch_ring(const MatList& ml, const void* src, int bpr, int depth, int sms, cudaStream_t stream) {
     const size_t smem = (size_t)ring_record_bytes(bpr) + (size_t)kGemvWarps * depth * ring_stage_bytes(bpr, R);
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(matvec_q4k_ring_kernel<R, FROM_X>,
+        cudaError_t e = cudaFuncSetAttribute(matvec_q4k_ring_kernel<R, FROM_X, PEER>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmemBudget);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
@@ -276,7 +279,7 @@ cudaError_t launch_ring(const MatList& ml, const void* src, int bpr, int depth, 
     int groups = 0;
     for (int i = 0; i < ml.n; ++i) groups += (ml.rows[i] + R - 1) / R;
     const int grid = groups < sms ? groups : sms;  // row groups go to warp slots warp-major
-    return mg::launch_pdl(matvec_q4k_ring_kernel<R, FROM_X>, dim3((unsigned)grid), dim3(kGemvThreads), smem, stream,
+    return mg::launch_pdl(matvec_q4k_ring_kernel<R, FROM_X, PEER>, dim3((unsigned)grid), dim3(kGemvThreads), smem, stream,
                           ml, src, mg::aligned16(src) ? 1 : 0, bpr, depth);
 }
 
@@ -284,8 +287,17 @@ cudaError_t launch_ring(const MatList& ml, const void* src, int bpr, int depth, 
 template <int R, int FROM_X>
 cudaError_t launch_gemv(const MatList& ml, const void* src, int bpr, int sms, cudaStream_t stream) {
     const int depth = ring_depth(bpr, R);
-    if (depth >= 2) return launch_ring<R, FROM_X>(ml, src, bpr, depth, sms, stream);
-    return launch_dp4a<R, FROM_X>(ml, src, bpr, sms, stream);
+    const bool stamped = (ml.peer.world > 1 && ml.peer.stamp_slots != nullptr) || ml.xin.slots != nullptr;
+    const bool fused = ml.peer.world > 1 && ml.peer.stamp_slots == nullptr;
+    if (stamped && fused) return cudaErrorInvalidValue;  // a stamped input with a handshake output: not built
+    if (depth >= 2) {
+        if (stamped) return launch_ring<R, FROM_X, kPeerStamped>(ml, src, bpr, depth, sms, stream);
+        if (fused) return launch_ring<R, FROM_X, kPeerFused>(ml, src, bpr, depth, sms, stream);
+        return launch_ring<R, FROM_X, kPeerNone>(ml, src, bpr, depth, sms, stream);
+    }
+    if (stamped) return launch_dp4a<R, FROM_X, kPeerStamped>(ml, src, bpr, sms, stream);
+    if (fused) return launch_dp4a<R, FROM_X, kPeerFused>(ml, src, bpr, sms, stream);
+    return launch_dp4a<R, FROM_X, kPeerNone>(ml, src, bpr, sms, stream);
 }
 
 // Per (device, stream) scratch for the limb records of long activation vectors.  Every kernel of
@@ -397,7 +409,7 @@ extern "C" int mg_q4k_x_to_limbs_on_stream(const float* x, int k, void* records,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, x_to_limbs_kernel, x, (const float*)nullptr, (float*)nullptr,
+    return (int)cudaLaunchKernelEx(&cfg, x_to_limbs_kernel<kPeerNone>, x, (const float*)nullptr, (float*)nullptr,
                                    static_cast<uint32_t*>(records), threads,
                                    ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) ? 1 : 0,
                                    mg::early_trigger_flag() ? 0 : 1, mgpeer::PeerSync{});
@@ -422,7 +434,13 @@ extern "C" int mg_swiglu_limbs_on_stream(const float* gate, const float* up, flo
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const int aligned = (mg::aligned16(gate) && mg::aligned16(up)) ? 1 : 0;
-    return (int)cudaLaunchKernelEx(&cfg, x_to_limbs_kernel, gate, up, act_out, static_cast<uint32_t*>(records),
+    if (peer.world > 1 && peer.stamp_slots != nullptr)
+        return (int)cudaLaunchKernelEx(&cfg, x_to_limbs_kernel<kPeerStamped>, gate, up, act_out, static_cast<uint32_t*>(records),
+                                       threads, aligned, mg::early_trigger_flag() ? 0 : 1, peer);
+    if (peer.world > 1)
+        return (int)cudaLaunchKernelEx(&cfg, x_to_limbs_kernel<kPeerFused>, gate, up, act_out, static_cast<uint32_t*>(records),
+                                       threads, aligned, mg::early_trigger_flag() ? 0 : 1, peer);
+    return (int)cudaLaunchKernelEx(&cfg, x_to_limbs_kernel<kPeerNone>, gate, up, act_out, static_cast<uint32_t*>(records),
                                    threads, aligned, mg::early_trigger_flag() ? 0 : 1, peer);
 }
 
@@ -517,7 +535,13 @@ extern "C" int mg_matvec_q4k_bias_on_stream(const uint8_t* w_q4, const float* x,
     // Matrices of many short rows go to the tensor-core kernel (half an SM per CTA, speculative
     // start: consecutive launches overlap); few rows or long rows are faster on the dp4a ring
     // kernel below, whose x conversion is lighter.
-    const bool want_mma = (out_dim >= kMmaMinRows && gemvmma::fits_half_sm(blocks_per_row)) || !limbs_path_ok(blocks_per_row);
+    // Measured (graph-replayed chains, rotating weight copies): 18944 x 3584 9.6 against 12.3 us, 8192 x 8192
+    // 12.2 against 14.0 us, 28672 x 8192 27.0 against 31.3 us in favour of the tensor-core kernel (the last two
+    // with three windows per row and one CTA per SM); rows of 18944 and 28672 weights (down projections)
+    // 18.6 against 17.3 and 52.8 against 36.1 us in favour of the ring kernel.
+    const bool want_mma = (out_dim >= kMmaMinRows &&
+                           (gemvmma::fits_half_sm(blocks_per_row) || blocks_per_row <= kFusedConvertMaxBpr)) ||
+                          !limbs_path_ok(blocks_per_row);
     if (peer.world <= 1 && want_mma && gemvmma::supported(blocks_per_row)) {
         // the tensor-core kernel: one launch, x converted inside, no scratch
         const mg::DeviceProps& dp = mg::device_props();
