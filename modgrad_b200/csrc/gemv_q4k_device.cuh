@@ -133,12 +133,6 @@ __device__ __forceinline__ void load_chunk(float (&v)[4], const float* x, int ch
     }
 }
 
-// Four consecutive activations out of a stamped vector: each slot is polled until it carries `epoch`.
-__device__ __forceinline__ void load_chunk_stamped(float (&v)[4], const mgpeer::StampIn& in, int chunk, unsigned epoch) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(mgpeer::ld_stamped(in, (long long)chunk * 4 + i, epoch));
-}
-
 // ---------------------------------------------------------------------------------------------
 // The streaming GEMV on limb records.
 // ---------------------------------------------------------------------------------------------
@@ -317,14 +311,27 @@ __device__ __forceinline__ void stage_records(const MatList& ml, const void* src
         const int n_chunks = bpr * 64;  // multiple of 64: whole warps stay in or out of range
         constexpr int kU = 4;
         float v[kU][4];
+        if (PEER == kPeerStamped && ml.xin.slots != nullptr) {
+            // the thread's sixteen activations out of a stamped vector, polled together
+            long long idx[kU * 4];
+            unsigned bits[kU * 4], live = 0u;
 #pragma unroll
-        for (int u = 0; u < kU; ++u) {
-            const int c = threadIdx.x + u * kGemvThreads;
-            if (c < n_chunks) {
-                if (PEER == kPeerStamped && ml.xin.slots != nullptr)
-                    load_chunk_stamped(v[u], ml.xin, c, mgpeer::exchange_epoch(ml.xin.epoch_dev, ml.xin.epoch_mul, ml.xin.epoch_add));
-                else
-                    load_chunk<COHERENT>(v[u], x, c, x_aligned);
+            for (int u = 0; u < kU; ++u) {
+                const int c = threadIdx.x + u * kGemvThreads;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) idx[u * 4 + i] = (long long)c * 4 + i;
+                if (c < n_chunks) live |= 0xFu << (4 * u);
+            }
+            mgpeer::ld_stamped_n<kU * 4>(ml.xin, idx, live, mgpeer::exchange_epoch(ml.xin.epoch_dev, ml.xin.epoch_mul, ml.xin.epoch_add), bits);
+#pragma unroll
+            for (int u = 0; u < kU; ++u)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[u][i] = __uint_as_float(bits[u * 4 + i]);
+        } else {
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+                const int c = threadIdx.x + u * kGemvThreads;
+                if (c < n_chunks) load_chunk<COHERENT>(v[u], x, c, x_aligned);
             }
         }
         if (ml.norm_w != nullptr) {
@@ -369,13 +376,22 @@ __device__ __forceinline__ void stage_records(const MatList& ml, const void* src
         const int n_vec = bpr * 4 * xlimbs::kRecordVec4;
         if (PEER == kPeerStamped && ml.xin.slots != nullptr) {  // stamped records: one slot per record word
             const unsigned epoch = mgpeer::exchange_epoch(ml.xin.epoch_dev, ml.xin.epoch_mul, ml.xin.epoch_add);
-            for (int i = threadIdx.x; i < n_vec; i += kGemvThreads) {
-                uint4 w;
-                w.x = mgpeer::ld_stamped(ml.xin, (long long)i * 4 + 0, epoch);
-                w.y = mgpeer::ld_stamped(ml.xin, (long long)i * 4 + 1, epoch);
-                w.z = mgpeer::ld_stamped(ml.xin, (long long)i * 4 + 2, epoch);
-                w.w = mgpeer::ld_stamped(ml.xin, (long long)i * 4 + 3, epoch);
-                rec_s[i] = w;
+            for (int base = threadIdx.x; base < n_vec; base += 4 * kGemvThreads) {  // four record vectors per round
+                long long idx[16];
+                unsigned bits[16], live = 0u;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = base + j * kGemvThreads;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) idx[j * 4 + k] = (long long)i * 4 + k;
+                    if (i < n_vec) live |= 0xFu << (4 * j);
+                }
+                mgpeer::ld_stamped_n<16>(ml.xin, idx, live, epoch, bits);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = base + j * kGemvThreads;
+                    if (i < n_vec) rec_s[i] = make_uint4(bits[j * 4], bits[j * 4 + 1], bits[j * 4 + 2], bits[j * 4 + 3]);
+                }
             }
         } else {
             for (int i = threadIdx.x; i < n_vec; i += kGemvThreads) cp_async16(&rec_s[i], &rec_g[i]);

@@ -162,10 +162,18 @@ __global__ void __launch_bounds__(1024) rms_norm_stamped_kernel(const mgpeer::St
     __shared__ float red[33];
     const unsigned epoch = mgpeer::exchange_epoch(in.epoch_dev, in.epoch_mul, in.epoch_add);
     float v[8], p = 0.0f;  // n <= 8192
-    for (int k = 0; k < 8; ++k) {
-        const int i = threadIdx.x + k * 1024;
-        v[k] = i < n ? __uint_as_float(mgpeer::ld_stamped(in, i, epoch)) : 0.0f;
-        p = fmaf(v[k], v[k], p);
+    {
+        long long idx[8];
+        unsigned bits[8], live = 0u;
+        for (int k = 0; k < 8; ++k) {
+            idx[k] = threadIdx.x + k * 1024;
+            if (idx[k] < n) live |= 1u << k;
+        }
+        mgpeer::ld_stamped_n<8>(in, idx, live, epoch, bits);
+        for (int k = 0; k < 8; ++k) {
+            v[k] = ((live >> k) & 1u) ? __uint_as_float(bits[k]) : 0.0f;
+            p = fmaf(v[k], v[k], p);
+        }
     }
     for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(0xFFFFFFFFu, p, o);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = p;

@@ -113,6 +113,40 @@ __device__ __forceinline__ unsigned ld_stamped(const StampIn& in, long long inde
     }
 }
 
+// N slots at once: the loads of a round are all in flight together (a lone poll is a round trip to
+// L2 at system scope, ~0.6 us; sixteen of them one after the other were most of a consumer's staging
+// time); rounds repeat until every live slot carries `epoch`, bounded as above.  bits[i] = 0 on failure.
+template <int N>
+__device__ __forceinline__ void ld_stamped_n(const StampIn& in, const long long (&index)[N], unsigned live_mask,
+                                             unsigned epoch, unsigned (&bits)[N]) {
+    unsigned spins = 0;
+    for (;;) {
+        unsigned long long v[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+            v[i] = ((live_mask >> i) & 1u) ? ld_stamped_raw(in.slots + index[i]) : ((unsigned long long)epoch << 32);
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+            ok = ok && (unsigned)(v[i] >> 32) == epoch;
+            bits[i] = (unsigned)v[i];
+        }
+        if (ok) return;
+        if ((++spins & 255u) == 0) {
+            bool give_up = *reinterpret_cast<volatile unsigned*>(in.err) != 0u;
+            if (!give_up && spins > in.spin_limit) {
+                atomicCAS(in.err, 0u, (unsigned)in.site + 1u);
+                give_up = true;
+            }
+            if (give_up) {
+#pragma unroll
+                for (int i = 0; i < N; ++i) bits[i] = 0u;
+                return;
+            }
+        }
+    }
+}
+
 // Called by ALL threads of EVERY CTA of the grid after their last peer store.  The last CTA to
 // arrive publishes this rank's epoch on every peer and waits (bounded) for the peers' epochs; the
 // grid therefore completes only when the whole gathered buffer is in local memory.
