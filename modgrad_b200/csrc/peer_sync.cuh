@@ -132,6 +132,9 @@ __device__ __forceinline__ void ld_stamped_n(const StampIn& in, const long long 
             bits[i] = (unsigned)v[i];
         }
         if (ok) return;
+        // Not all here yet: back off before the next round.  Every thread of every CTA polls, and rounds
+        // issued back to back would keep L2 busy with polls while the weight streams need it.
+        __nanosleep(128);
         if ((++spins & 255u) == 0) {
             bool give_up = *reinterpret_cast<volatile unsigned*>(in.err) != 0u;
             if (!give_up && spins > in.spin_limit) {
