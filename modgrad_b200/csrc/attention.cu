@@ -277,6 +277,94 @@ __global__ void rope_append_f16_kernel(float* q, float* k, const float* v,
 
 constexpr int kMaxSplitsOneLaunch = 160;  // one split per SM and KV head at most
 
+// The last CTA of a KV head to get here (ticket counter, left at zero for the next launch) merges the
+// per-split partials of the group's heads and writes the output, with the exchange's stores where one
+// is set.  Called by all threads of every CTA after they have written their partials.
+template <int HD, int GRP>
+__device__ __forceinline__ void merge_splits_last_cta(const float* partial, unsigned* counters, float* out, int kv_h,
+                                                      int n_splits, const mgpeer::PeerSync& peer,
+                                                      float (*wsplit)[kMaxSplitsOneLaunch], float* lsum, int* is_last_p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int& is_last = *is_last_p;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned ticket = atomicAdd(counters + kv_h, 1u);
+        is_last = ticket == (unsigned)n_splits - 1u;
+        if (is_last) counters[kv_h] = 0;  // every CTA of the head has taken its ticket: ready for the next launch
+    }
+    __syncthreads();
+    if (is_last) {
+        __threadfence();
+        const int stride = HD + 2;
+        // weights of the splits: warp g serves head g of the group (all heads at once)
+        for (int g = warp; g < GRP; g += 8) {
+            const float* pp = partial + (size_t)(kv_h * GRP + g) * n_splits * stride;
+            float mloc = -INFINITY;
+            for (int sidx = lane; sidx < n_splits; sidx += 32) {
+                const float ms = __ldcg(pp + (size_t)sidx * stride);
+                wsplit[g][sidx] = ms;
+                mloc = fmaxf(mloc, ms);
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, off));
+            float lloc = 0.0f;
+            for (int sidx = lane; sidx < n_splits; sidx += 32) {
+                const float ms = wsplit[g][sidx];
+                const float w = ms > -INFINITY ? expf(ms - mloc) : 0.0f;
+                wsplit[g][sidx] = w;
+                lloc = fmaf(__ldcg(pp + (size_t)sidx * stride + 1), w, lloc);
+            }
+            lloc = q4k::warp_sum(lloc);
+            if (lane == 0) lsum[g] = lloc;
+        }
+        __syncthreads();
+        // thread -> (head g, four consecutive dims): 8-byte loads (rows of HD + 2 floats are 8-byte
+        // aligned), four splits in flight
+        for (int idx = threadIdx.x; idx < GRP * (HD / 4); idx += blockDim.x) {
+            const int g = idx / (HD / 4), d = (idx % (HD / 4)) * 4;
+            const int h = kv_h * GRP + g;
+            const float* pp = partial + (size_t)h * n_splits * stride + 2 + d;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            int sidx = 0;
+            for (; sidx + 4 <= n_splits; sidx += 4) {
+                float2 lo[4], hi[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2* src = reinterpret_cast<const float2*>(pp + (size_t)(sidx + j) * stride);
+                    lo[j] = __ldcg(src);
+                    hi[j] = __ldcg(src + 1);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float w = wsplit[g][sidx + j];
+                    acc[0] = fmaf(lo[j].x, w, acc[0]); acc[1] = fmaf(lo[j].y, w, acc[1]);
+                    acc[2] = fmaf(hi[j].x, w, acc[2]); acc[3] = fmaf(hi[j].y, w, acc[3]);
+                }
+            }
+            for (; sidx < n_splits; ++sidx) {
+                const float2* src = reinterpret_cast<const float2*>(pp + (size_t)sidx * stride);
+                const float2 lo = __ldcg(src), hi = __ldcg(src + 1);
+                const float w = wsplit[g][sidx];
+                acc[0] = fmaf(lo.x, w, acc[0]); acc[1] = fmaf(lo.y, w, acc[1]);
+                acc[2] = fmaf(hi.x, w, acc[2]); acc[3] = fmaf(hi.y, w, acc[3]);
+            }
+            const float inv_den = lsum[g];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float r = acc[e] / inv_den;
+                const size_t o_idx = (size_t)h * HD + d + e;
+                if (peer.world > 1 && peer.stamp_slots != nullptr) {
+                    out[o_idx] = r;
+                    mgpeer::store_stamped_all(peer, (long long)o_idx, __float_as_uint(r),
+                                              mgpeer::exchange_epoch(peer.epoch_dev, peer.epoch_mul, peer.epoch_add));
+                } else if (peer.world > 1) mgpeer::store_all(peer, out + o_idx, r);
+                else out[o_idx] = r;
+            }
+        }
+    }
+}
+
 // ---- one launch per layer: RoPE + cache append + split attention + merge ---------------------------
 // q, k_new, v_new arrive as the projections left them (f32, not rotated).  Every CTA (KV head, split)
 // rotates the query heads of its group in registers; the CTA whose split holds the new position
@@ -413,85 +501,223 @@ sdpa_rope_split_f16_kernel(const float* q, const float* k_new, const float* v_ne
         if (d == 0) { dst[0] = M; dst[1] = L; }
         dst[2 + d] = acc;
     }
-    // ---- the last CTA of this KV head merges the splits ---------------------------------------------------
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned ticket = atomicAdd(counters + kv_h, 1u);
-        is_last = ticket == (unsigned)n_splits - 1u;
-        if (is_last) counters[kv_h] = 0;  // every CTA of the head has taken its ticket: ready for the next launch
-    }
-    __syncthreads();
-    if (is_last) {
-        __threadfence();
-        const int stride = HD + 2;
-        // weights of the splits: warp g serves head g of the group (all heads at once)
-        for (int g = warp; g < GRP; g += 8) {
-            const float* pp = partial + (size_t)(kv_h * GRP + g) * n_splits * stride;
-            float mloc = -INFINITY;
-            for (int sidx = lane; sidx < n_splits; sidx += 32) {
-                const float ms = __ldcg(pp + (size_t)sidx * stride);
-                wsplit[g][sidx] = ms;
-                mloc = fmaxf(mloc, ms);
-            }
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, off));
-            float lloc = 0.0f;
-            for (int sidx = lane; sidx < n_splits; sidx += 32) {
-                const float ms = wsplit[g][sidx];
-                const float w = ms > -INFINITY ? expf(ms - mloc) : 0.0f;
-                wsplit[g][sidx] = w;
-                lloc = fmaf(__ldcg(pp + (size_t)sidx * stride + 1), w, lloc);
-            }
-            lloc = q4k::warp_sum(lloc);
-            if (lane == 0) lsum[g] = lloc;
-        }
-        __syncthreads();
-        // thread -> (head g, four consecutive dims): 8-byte loads (rows of HD + 2 floats are 8-byte
-        // aligned), four splits in flight
-        for (int idx = threadIdx.x; idx < GRP * (HD / 4); idx += blockDim.x) {
-            const int g = idx / (HD / 4), d = (idx % (HD / 4)) * 4;
-            const int h = kv_h * GRP + g;
-            const float* pp = partial + (size_t)h * n_splits * stride + 2 + d;
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            int sidx = 0;
-            for (; sidx + 4 <= n_splits; sidx += 4) {
-                float2 lo[4], hi[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float2* src = reinterpret_cast<const float2*>(pp + (size_t)(sidx + j) * stride);
-                    lo[j] = __ldcg(src);
-                    hi[j] = __ldcg(src + 1);
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float w = wsplit[g][sidx + j];
-                    acc[0] = fmaf(lo[j].x, w, acc[0]); acc[1] = fmaf(lo[j].y, w, acc[1]);
-                    acc[2] = fmaf(hi[j].x, w, acc[2]); acc[3] = fmaf(hi[j].y, w, acc[3]);
-                }
-            }
-            for (; sidx < n_splits; ++sidx) {
-                const float2* src = reinterpret_cast<const float2*>(pp + (size_t)sidx * stride);
-                const float2 lo = __ldcg(src), hi = __ldcg(src + 1);
-                const float w = wsplit[g][sidx];
-                acc[0] = fmaf(lo.x, w, acc[0]); acc[1] = fmaf(lo.y, w, acc[1]);
-                acc[2] = fmaf(hi.x, w, acc[2]); acc[3] = fmaf(hi.y, w, acc[3]);
-            }
-            const float inv_den = lsum[g];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float r = acc[e] / inv_den;
-                const size_t o_idx = (size_t)h * HD + d + e;
-                if (peer.world > 1 && peer.stamp_slots != nullptr) {
-                    out[o_idx] = r;
-                    mgpeer::store_stamped_all(peer, (long long)o_idx, __float_as_uint(r),
-                                              mgpeer::exchange_epoch(peer.epoch_dev, peer.epoch_mul, peer.epoch_add));
-                } else if (peer.world > 1) mgpeer::store_all(peer, out + o_idx, r);
-                else out[o_idx] = r;
-            }
-        }
-    }
+    merge_splits_last_cta<HD, GRP>(partial, counters, out, kv_h, n_splits, peer, wsplit, lsum, &is_last);
     mgpeer::peer_finish(peer);  // all-gather of the heads: the grid ends when every rank's heads are here
+}
+
+// ---- the same launch with the per-position arithmetic on the tensor cores (head_dim 128) -------------------
+// A warp takes sixteen positions per step: S = Q . K^T and O += P . V as mma.sync.m16n8k16 (f16 in, f32
+// accumulate) with the group's query heads as rows 0 .. GRP-1 of the 16-row operand (rows 8-15 are
+// zero).  K and V are exact halves (the cache); Q (rotated, scaled) and P are split into two half limbs
+// each (hi + lo, 22 significant bits), so every product is exact in f32 and the result stays within
+// rounding of the scalar kernel.  K fragments come straight from the cache (half2 along dims), V
+// goes through a per-warp shared-memory tile and ldmatrix.trans.  The new token's K/V row is written
+// to the cache first (one warp, then a CTA barrier) and read back like any other row.
+// Rows 8-15 of the A operand are zero in this kernel, so rows 8-15 of every accumulator stay zero: all
+// MMAs share one pair of scratch registers for them (z).
+__device__ __forceinline__ void mma_f16_16816(float (&c)[2], float (&z)[2], uint32_t a0, uint32_t a2, uint32_t b0,
+                                              uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(z[0]), "+f"(z[1])
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void split_half2(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const __half hx = __float2half_rn(x), hy = __float2half_rn(y);
+    const __half lx = __float2half_rn(x - __half2float(hx)), ly = __float2half_rn(y - __half2float(hy));
+    hi = (uint32_t)__half_as_ushort(hx) | ((uint32_t)__half_as_ushort(hy) << 16);
+    lo = (uint32_t)__half_as_ushort(lx) | ((uint32_t)__half_as_ushort(ly) << 16);
+}
+
+template <int GRP>
+__global__ void __launch_bounds__(256, 1)
+sdpa_rope_mma_f16_kernel(const float* q, const float* k_new, const float* v_new, __half* k_cache, __half* v_cache,
+                         float* partial, unsigned* counters, float* out, const int* pos_dev, int pos_arg,
+                         int n_kv_heads, int kv_dim, float scale, int n_splits, float rope_base,
+                         const float* freq_table, int hold_trigger, const mgpeer::PeerSync peer) {
+    mg::pdl_prologue(hold_trigger);
+    constexpr int HD = 128, HALF = 64, kVStride = HD + 8;  // halves per tile row: 272 bytes, conflict-free ldmatrix
+    // The V tiles of the eight warps and the merge buffer are used one after the other: one array.
+    constexpr int kTileHalves = 16 * kVStride;
+    constexpr int kMergeFloats = 8 * GRP * (HD + 2);
+    constexpr int kUnionBytes = (8 * kTileHalves * 2 > kMergeFloats * 4) ? 8 * kTileHalves * 2 : kMergeFloats * 4;
+    __shared__ __align__(16) unsigned char un[kUnionBytes];
+    __shared__ float cs[HALF], sn[HALF];
+    __shared__ float wsplit[GRP][kMaxSplitsOneLaunch];
+    __shared__ float lsum[GRP];
+    __shared__ int is_last;
+    const int kv_h = blockIdx.x, split = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = pos_dev ? *pos_dev : pos_arg;
+    const int seq_len = pos + 1;
+    const int chunk = (seq_len + n_splits - 1) / n_splits;
+    const int t0 = split * chunk, t1 = min(seq_len, t0 + chunk);
+    const bool has_new = pos >= t0 && pos < t1;
+
+    if (threadIdx.x < HALF) {
+        const int i = threadIdx.x;
+        // f64 pow rounded once: matches a correctly rounded powf (angles reach thousands of radians)
+        const float freq = freq_table ? freq_table[i] : (float)pow((double)rope_base, (double)(-2.0f * (float)i / (float)HD));
+        sincosf((float)pos * freq, &sn[i], &cs[i]);
+    }
+    __syncthreads();
+    auto rot = [&](const float* vec, int d) -> float {  // element d of the rotated vector
+        const int i = d & (HALF - 1);
+        return d < HALF ? vec[d] * cs[i] - vec[d + HALF] * sn[i] : vec[d - HALF] * sn[i] + vec[d] * cs[i];
+    };
+    if (has_new && warp == 0) {  // the new token's row: lane owns dims 4*lane .. 4*lane+3
+        const size_t off = (size_t)pos * kv_dim + (size_t)kv_h * HD + lane * 4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            k_cache[off + e] = __float2half_rn(rot(k_new + (size_t)kv_h * HD, lane * 4 + e));
+            v_cache[off + e] = __float2half_rn(v_new[(size_t)kv_h * HD + lane * 4 + e]);
+        }
+    }
+    __syncthreads();  // the row is read back below by every warp of this CTA (cache-global loads)
+
+    // Q fragments of head g = lane / 4 (rows 8-15 of the operand are zero): chunk c holds dims
+    // 16c + 2(lane%4) + {0,1} (a0) and + 8 (a2), as hi and lo limbs.
+    const int g = lane >> 2, tq = lane & 3;
+    uint32_t qh0[8], qh2[8], ql0[8], ql2[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        float x[4] = {0.f, 0.f, 0.f, 0.f};
+        if (g < GRP) {
+            const float* qv = q + (size_t)(kv_h * GRP + g) * HD;
+            const int d0 = c * 16 + tq * 2;
+            x[0] = rot(qv, d0) * scale; x[1] = rot(qv, d0 + 1) * scale;
+            x[2] = rot(qv, d0 + 8) * scale; x[3] = rot(qv, d0 + 9) * scale;
+        }
+        split_half2(x[0], x[1], qh0[c], ql0[c]);
+        split_half2(x[2], x[3], qh2[c], ql2[c]);
+    }
+    float o[16][2], z[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nb = 0; nb < 16; ++nb) { o[nb][0] = o[nb][1] = 0.f; }
+    float m = -INFINITY, l = 0.f;  // of head g (the four lanes of a head hold the same values)
+
+    __half* tile = reinterpret_cast<__half*>(un) + warp * kTileHalves;
+    const uint32_t tile_s = (uint32_t)__cvta_generic_to_shared(tile);
+    const __half* kbase = k_cache + (size_t)kv_h * HD;
+    const __half* vbase = v_cache + (size_t)kv_h * HD;
+    for (int tb = t0 + warp * 16; tb < t1; tb += 8 * 16) {
+        // ---- V rows tb .. tb+15 -> the warp's tile (rows past the end repeat the last valid row: p = 0 there)
+        {
+            const int r = lane >> 1, hsel = lane & 1;
+            const int t = min(tb + r, t1 - 1);
+            const __half* src = vbase + (size_t)t * kv_dim + hsel * 64;
+            const uint32_t dst = tile_s + (uint32_t)(r * kVStride + hsel * 64) * 2u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + j * 16), "l"(src + j * 8) : "memory");
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        // ---- S = Q . K^T for the two blocks of eight positions
+        float s0[2] = {0.f, 0.f}, s1[2] = {0.f, 0.f}, s0l[2] = {0.f, 0.f}, s1l[2] = {0.f, 0.f};
+        {
+            const int ta = min(tb + g, t1 - 1), tb2 = min(tb + 8 + g, t1 - 1);  // B fragment: position = lane / 4
+            const uint32_t* ka = reinterpret_cast<const uint32_t*>(kbase + (size_t)ta * kv_dim) + tq;
+            const uint32_t* kb = reinterpret_cast<const uint32_t*>(kbase + (size_t)tb2 * kv_dim) + tq;
+            uint32_t fa[16], fb[16];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {  // dims 16c + 2tq (+8): words 8c + tq and 8c + 4 + tq of the row
+                fa[2 * c] = __ldcg(ka + 8 * c); fa[2 * c + 1] = __ldcg(ka + 8 * c + 4);
+                fb[2 * c] = __ldcg(kb + 8 * c); fb[2 * c + 1] = __ldcg(kb + 8 * c + 4);
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                mma_f16_16816(s0, z, qh0[c], qh2[c], fa[2 * c], fa[2 * c + 1]);
+                mma_f16_16816(s0l, z, ql0[c], ql2[c], fa[2 * c], fa[2 * c + 1]);
+                mma_f16_16816(s1, z, qh0[c], qh2[c], fb[2 * c], fb[2 * c + 1]);
+                mma_f16_16816(s1l, z, ql0[c], ql2[c], fb[2 * c], fb[2 * c + 1]);
+            }
+            s0[0] += s0l[0]; s0[1] += s0l[1]; s1[0] += s1l[0]; s1[1] += s1l[1];
+        }
+        // ---- online softmax of head g over the sixteen positions: this lane holds positions
+        //      tb + 2tq + {0,1} (s0) and tb + 8 + 2tq + {0,1} (s1)
+        float sc[4] = {s0[0], s0[1], s1[0], s1[1]};
+        const int tp[4] = {tb + 2 * tq, tb + 2 * tq + 1, tb + 8 + 2 * tq, tb + 9 + 2 * tq};
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (tp[i] >= t1) sc[i] = -INFINITY;
+            mx = fmaxf(mx, sc[i]);
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+        const float m_new = fmaxf(m, mx);  // finite: every step has at least one valid position
+        const float a = expf(m - m_new);
+        float pr[4], ps = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { pr[i] = expf(sc[i] - m_new); ps += pr[i]; }
+        ps += __shfl_xor_sync(0xFFFFFFFFu, ps, 1);
+        ps += __shfl_xor_sync(0xFFFFFFFFu, ps, 2);
+        l = fmaf(l, a, ps);
+        m = m_new;
+#pragma unroll
+        for (int nb = 0; nb < 16; ++nb) { o[nb][0] *= a; o[nb][1] *= a; }
+        uint32_t ph0, pl0, ph2, pl2;
+        split_half2(pr[0], pr[1], ph0, pl0);
+        split_half2(pr[2], pr[3], ph2, pl2);
+        // ---- O += P . V
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+        {
+            const int mat = lane >> 3, r = lane & 7;  // ldmatrix: lane supplies row r of matrix mat
+            const uint32_t row_addr = tile_s + (uint32_t)((((mat & 1) * 8 + r) * kVStride) + (mat >> 1) * 8) * 2u;
+#pragma unroll
+            for (int nb = 0; nb < 16; nb += 2) {
+                uint32_t v0, v1, v2, v3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+                             : "r"(row_addr + (uint32_t)nb * 16u));
+                // The tensor cores truncate when they add into the accumulator; chained over the ~150 steps
+                // of a long context that bias reached 1e-5.  Each step therefore multiplies into a zeroed
+                // accumulator and is added to the running sum with an ordinary (rounded) f32 add.
+                float t0[2] = {0.f, 0.f}, t1v[2] = {0.f, 0.f};
+                mma_f16_16816(t0, z, pl0, pl2, v0, v1);
+                mma_f16_16816(t0, z, ph0, ph2, v0, v1);
+                mma_f16_16816(t1v, z, pl0, pl2, v2, v3);
+                mma_f16_16816(t1v, z, ph0, ph2, v2, v3);
+                o[nb][0] += t0[0]; o[nb][1] += t0[1];
+                o[nb + 1][0] += t1v[0]; o[nb + 1][1] += t1v[1];
+            }
+        }
+        __syncwarp();  // the tile is refilled by the next step
+    }
+    // ---- the warp's (m, l, o) of heads 0 .. GRP-1 -> the merge buffer (the V tiles are dead)
+    __syncthreads();
+    float (*sh)[GRP][HD + 2] = reinterpret_cast<float (*)[GRP][HD + 2]>(un);
+    if (g < GRP) {
+        if (tq == 0) { sh[warp][g][0] = m; sh[warp][g][1] = l; }
+#pragma unroll
+        for (int nb = 0; nb < 16; ++nb) {
+            sh[warp][g][2 + nb * 8 + tq * 2] = o[nb][0];
+            sh[warp][g][2 + nb * 8 + tq * 2 + 1] = o[nb][1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < GRP * HD; idx += blockDim.x) {
+        const int gg = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) M = fmaxf(M, sh[w][gg][0]);
+        float L = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const float mw = sh[w][gg][0];
+            if (mw > -INFINITY) {
+                const float fw = expf(mw - M);
+                L = fmaf(sh[w][gg][1], fw, L);
+                acc = fmaf(sh[w][gg][2 + d], fw, acc);
+            }
+        }
+        float* dst = partial + ((size_t)(kv_h * GRP + gg) * n_splits + split) * (HD + 2);
+        if (d == 0) { dst[0] = M; dst[1] = L; }
+        dst[2 + d] = acc;
+    }
+    merge_splits_last_cta<HD, GRP>(partial, counters, out, kv_h, n_splits, peer, wsplit, lsum, &is_last);
+    mgpeer::peer_finish(peer);
 }
 
 template <int EPL>
@@ -647,6 +873,19 @@ int mg_sdpa_rope_decode_f16kv_on_stream(const float* q, const float* k_new, cons
     const size_t part_bytes = ((size_t)n_heads * n_splits * (head_dim + 2) * sizeof(float) + 255) & ~(size_t)255;
     unsigned* counters = reinterpret_cast<unsigned*>(static_cast<unsigned char*>(scratch) + part_bytes);
     const int hold = mg::early_trigger_flag() ? 0 : 1;
+    if (head_dim == 128 && grp <= 8) {
+#define MG_MMA_CASE(G)                                                                                            \
+    case G:                                                                                                       \
+        return (int)mg::launch_pdl(sdpa_rope_mma_f16_kernel<G>, grid, dim3(256), 0, s, q, k_new, v_new, k, v, part, \
+                                   counters, out, pos_dev, pos, n_kv_heads, kv_dim, scale, n_splits, rope_base,   \
+                                   freq_table, hold, peer);
+        switch (grp) {
+            MG_MMA_CASE(1) MG_MMA_CASE(2) MG_MMA_CASE(3) MG_MMA_CASE(4) MG_MMA_CASE(5) MG_MMA_CASE(6) MG_MMA_CASE(7)
+            MG_MMA_CASE(8)
+            default: break;
+        }
+#undef MG_MMA_CASE
+    }
     if (head_dim == 128)
         return (int)launch_rope_split<4>(grp, grid, s, q, k_new, v_new, k, v, part, counters, out, pos_dev, pos, n_kv_heads,
                                          kv_dim, scale, n_splits, rope_base, freq_table, hold, peer);
