@@ -543,6 +543,7 @@ sdpa_rope_mma_f16_kernel(const float* q, const float* k_new, const float* v_new,
     constexpr int kUnionBytes = (8 * kTileHalves * 2 > kMergeFloats * 4) ? 8 * kTileHalves * 2 : kMergeFloats * 4;
     __shared__ __align__(16) unsigned char un[kUnionBytes];
     __shared__ float cs[HALF], sn[HALF];
+    __shared__ float qs[GRP * HD];
     __shared__ float wsplit[GRP][kMaxSplitsOneLaunch];
     __shared__ float lsum[GRP];
     __shared__ int is_last;
@@ -560,6 +561,9 @@ sdpa_rope_mma_f16_kernel(const float* q, const float* k_new, const float* v_new,
         const float freq = freq_table ? freq_table[i] : (float)pow((double)rope_base, (double)(-2.0f * (float)i / (float)HD));
         sincosf((float)pos * freq, &sn[i], &cs[i]);
     }
+    // The group's query heads go through shared memory: building the fragments straight from global
+    // memory is 64 scattered loads per lane, which were most of this kernel's time at short contexts.
+    for (int i = threadIdx.x; i < GRP * HD; i += blockDim.x) qs[i] = q[(size_t)kv_h * GRP * HD + i];
     __syncthreads();
     auto rot = [&](const float* vec, int d) -> float {  // element d of the rotated vector
         const int i = d & (HALF - 1);
@@ -583,7 +587,7 @@ sdpa_rope_mma_f16_kernel(const float* q, const float* k_new, const float* v_new,
     for (int c = 0; c < 8; ++c) {
         float x[4] = {0.f, 0.f, 0.f, 0.f};
         if (g < GRP) {
-            const float* qv = q + (size_t)(kv_h * GRP + g) * HD;
+            const float* qv = qs + g * HD;
             const int d0 = c * 16 + tq * 2;
             x[0] = rot(qv, d0) * scale; x[1] = rot(qv, d0 + 1) * scale;
             x[2] = rot(qv, d0 + 8) * scale; x[3] = rot(qv, d0 + 9) * scale;

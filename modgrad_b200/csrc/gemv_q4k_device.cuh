@@ -337,6 +337,15 @@ __device__ __forceinline__ void stage_records(const MatList& ml, const void* src
         if (ml.norm_w != nullptr) {
             // RMSNorm in front of the matvec (crates/modgrad-device/src/kfd/llm.rs:921-928, Plain)
             __shared__ float red[kGemvWarps + 1];
+            // the norm weights are requested before the reduction's barriers, so that their trip to L2
+            // overlaps it instead of following it
+            float wv[kU][4];
+            const bool w_aligned = (reinterpret_cast<uintptr_t>(ml.norm_w) & 15u) == 0;
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+                const int c = threadIdx.x + u * kGemvThreads;
+                if (c < n_chunks) load_chunk<false>(wv[u], ml.norm_w, c, w_aligned);
+            }
             float p = 0.0f;
 #pragma unroll
             for (int u = 0; u < kU; ++u) {
@@ -359,10 +368,8 @@ __device__ __forceinline__ void stage_records(const MatList& ml, const void* src
             for (int u = 0; u < kU; ++u) {
                 const int c = threadIdx.x + u * kGemvThreads;
                 if (c < n_chunks) {
-                    float wv[4];
-                    load_chunk<false>(wv, ml.norm_w, c, (reinterpret_cast<uintptr_t>(ml.norm_w) & 15u) == 0);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) v[u][i] = v[u][i] * inv * wv[i];
+                    for (int i = 0; i < 4; ++i) v[u][i] = v[u][i] * inv * wv[u][i];
                 }
             }
         }
