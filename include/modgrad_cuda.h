@@ -94,6 +94,16 @@ int launch_matvec_q5k_on_stream(const uint8_t* w_q5, const float* x, float* y, i
 int launch_matvec_q6k(const uint8_t* w_q6, const float* x, float* y, int out_dim, int blocks_per_row);
 int launch_matvec_q6k_on_stream(const uint8_t* w_q6, const float* x, float* y, int out_dim, int blocks_per_row,
                                 void* stream);
+/* y[row] = (add ? add[row] : 0) + W[row] . x for a Q5_K (ggml_type 13) or Q6_K (14) weight: the matvec with
+ * the residual add the decode loop puts behind it (crates/modgrad-gemma/src/rocm_gemma.rs:470-475, :497-500)
+ * folded in; y may alias add.  x_kind 0: x is the f32 activation vector.  x_kind 1 (Q6_K only, weight
+ * 4-byte aligned, blocks_per_row * 832 bytes within one CTA's shared memory): x holds the limb records of
+ * mg_q4k_x_to_limbs_on_stream / mg_swiglu_limbs_on_stream, multiplied with dp4a.  launch_matvec_q6k takes
+ * the same integer path for rows of up to 32 blocks (it converts x itself) when the weight is 4-byte
+ * aligned: the result then carries the activations' rounding to 23 bits of each 32-element sub-block's
+ * largest element, like the Q4_K launchers'. */
+int mg_matvec_kquant_on_stream(int ggml_type, const uint8_t* w, const void* x, int x_kind, const float* add, float* y,
+                               int out_dim, int blocks_per_row, void* stream);
 int launch_matvec_q6k_dp4a(const uint8_t* w, const int8_t* xq, const float* xd, const float* xsum, float* y,
                            int out_dim, int bpr);
 int launch_matvec_q6k_dp4a_on_stream(const uint8_t* w, const int8_t* xq, const float* xd, const float* xsum,
@@ -263,6 +273,10 @@ int mg_sdpa_rope_decode_f16kv_on_stream(const float* q, const float* k_new, cons
  * matvec, llm.rs:478-492; in_dim % 256 == 0, <= 12288), embedding row lookup (llm.rs:898-918)
  * and first-maximum arg-max where NaN never wins (rocm_gemma.rs:34-41; scratch: 2048 bytes). */
 int mg_matvec_f16_on_stream(const void* w_f16, const float* x, float* y, int out_dim, int in_dim, void* stream);
+/* One row of a Q4_K (12) / Q5_K (13) / Q6_K (14) embedding table, dequantised bit-exactly as the bulk
+ * dequantisers do (the reference dequantises the row on the host: rocm_gemma.rs:316-323). */
+int mg_embed_kquant_on_stream(const void* table, int ggml_type, int token, const int* token_dev, float* out, int d_model,
+                              int vocab, void* stream);
 int mg_embed_f16_on_stream(const void* table_f16, int token, const int* token_dev, float* out, int d_model,
                            int vocab, void* stream);
 int mg_argmax_on_stream(const float* v, int n, int* out_token_dev, void* scratch, int* history, int* step_dev,
@@ -282,6 +296,15 @@ enum {
 };
 typedef struct mg_decoder mg_decoder;
 int mg_decoder_create(const mg_decoder_config* cfg, mg_decoder** out);
+/* Single-GPU engine whose tensors carry their own GGUF types, as real checkpoints mix them: the
+ * per-tensor dispatch of RocmGemma::qmatvec (crates/modgrad-gemma/src/rocm_gemma.rs:291-309).
+ * proj_types: n_layers * 7 type ids in the order q, k, v, o, gate, up, down, each 12 (Q4_K), 13 (Q5_K)
+ * or 14 (Q6_K); embed_type / head_type: 1 (F16) or one of the three.  mg_decoder_upload then expects
+ * the byte size of each tensor's type; mg_decoder_weight_type reports it (0 for the f32 norms).
+ * All-default types build the engine of mg_decoder_create. */
+int mg_decoder_create_typed(const mg_decoder_config* cfg, const int* proj_types, int embed_type, int head_type,
+                            mg_decoder** out);
+int mg_decoder_weight_type(const mg_decoder* d, int layer, int which);
 /* Row-sharded engine, one process per GPU (no counterpart in the reference, which has no
  * multi-device code): rank r of `world` holds the rows of its query heads, of its slice of
  * the FFN, the hidden state and the vocabulary, and uploads / prefills only those slices;

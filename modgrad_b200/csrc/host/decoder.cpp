@@ -41,7 +41,22 @@ struct Layer {
             *wdown = nullptr;
     float *attn_norm = nullptr, *ffn_norm = nullptr;
     __half *k_cache = nullptr, *v_cache = nullptr;
+    // GGUF tensor types of wq, wk, wv, wo, wgate, wup, wdown (12 Q4_K, 13 Q5_K, 14 Q6_K)
+    uint8_t type[7] = {12, 12, 12, 12, 12, 12, 12};
 };
+
+constexpr int kTypeF16 = 1, kTypeQ4K = 12, kTypeQ5K = 13, kTypeQ6K = 14;
+// Bytes of a [rows][cols] tensor of GGUF type `type` (cols a multiple of 256 for the K-quants);
+// 0 for a type the engine does not run.
+size_t typed_bytes(int type, size_t rows, size_t cols) {
+    switch (type) {
+        case kTypeF16: return rows * cols * 2;
+        case kTypeQ4K: return rows * (cols / 256) * 144;
+        case kTypeQ5K: return rows * (cols / 256) * 176;
+        case kTypeQ6K: return rows * (cols / 256) * 210;
+        default: return 0;
+    }
+}
 
 }  // namespace
 
@@ -50,7 +65,12 @@ struct mg_decoder {
     std::vector<Layer> layers;
     uint8_t* weights = nullptr;  // the one allocation that holds every weight tensor
     size_t weights_bytes = 0;
-    __half *embed = nullptr, *lm_head = nullptr;
+    __half *embed = nullptr, *lm_head = nullptr;  // raw bytes of embed_type / head_type (half by default)
+    int embed_type = 1, head_type = 1;            // GGUF type ids (1 = F16)
+    // Some tensor is not of the default type (a Q5_K / Q6_K projection, a quantised embedding or head):
+    // the token is then queued one projection per launch through the launchers of each type.
+    bool mixed = false;
+    int mixed_launches = 0;  // kernels the last queued token of that path launched
     float* out_norm = nullptr;
     float* rope_freq = nullptr;  // base^(-2i/head_dim), i < head_dim/2
     // activations
@@ -114,8 +134,6 @@ int dev_alloc(mg_decoder* d, T** out, size_t count) {
     *out = static_cast<T*>(p);
     return 0;
 }
-
-size_t q4k_bytes(int rows, int cols) { return (size_t)rows * (cols / 256) * MG_Q4K_BLOCK_BYTES; }
 
 // hidden += x (the residual add after a gathered projection output)
 __global__ void residual_add_kernel(float* h, const float* x, int n) {
@@ -234,6 +252,7 @@ int gather_heads(mg_decoder* d) {
 }
 
 int queue_token_impl(mg_decoder* d);
+int queue_token_mixed(mg_decoder* d);
 
 // Stamped exchanges: the epoch of exchange `site` of layer `layer` in the current token is
 // tokens_decoded * (4 * n_layers + 4) + 4 * layer + site + 1: unique, increasing, never 0 (a zeroed
@@ -264,6 +283,7 @@ mgpeer::StampIn stamp_in(mg_decoder* d, int site, const unsigned long long* slot
 // kernels, which may start as soon as their predecessor lets its successor launch: there the
 // kernels that feed a collective keep their trigger until they have finished.
 int queue_token(mg_decoder* d) {
+    if (d->mixed) return queue_token_mixed(d);
     if (d->world == 1 || d->peer) return queue_token_impl(d);  // the peer-store gathers are our own kernels
     const int before = mg_pdl_early_trigger(0);
     const int rc = queue_token_impl(d);
@@ -385,6 +405,128 @@ int queue_token_impl(mg_decoder* d) {
         mg::launch_pdl(argmax_pairs_kernel, dim3(1), dim3(1), 0, d->stream, (const float*)d->pair_buf, d->world, tok_dev, d->history, (const int*)step_dev);
     }
     mg::launch_pdl(advance_state_kernel, dim3(1), dim3(1), 0, d->stream, d->state);
+    if ((e = (int)cudaGetLastError())) return fail(d, e, "advance");
+    return 0;
+}
+
+// y = W x for one tensor of GGUF type `type` (the per-tensor dispatch of RocmGemma::qmatvec,
+// crates/modgrad-gemma/src/rocm_gemma.rs:291-309).
+int typed_matvec(mg_decoder* d, int type, const void* w, const float* x, float* y, int rows, int cols) {
+    const uint8_t* wb = static_cast<const uint8_t*>(w);
+    switch (type) {
+        case kTypeQ4K: return launch_matvec_q4k_on_stream(wb, x, y, rows, cols / 256, d->stream);
+        case kTypeQ5K: return launch_matvec_q5k_on_stream(wb, x, y, rows, cols / 256, d->stream);
+        case kTypeQ6K: return launch_matvec_q6k_on_stream(wb, x, y, rows, cols / 256, d->stream);
+        case kTypeF16: return mg_matvec_f16_on_stream(w, x, y, rows, cols, d->stream);
+        default: return (int)cudaErrorInvalidValue;
+    }
+}
+
+// y[i] = W[i] . rms_norm(hidden) for n tensors of one input.  All Q4_K: the one fused launch of the
+// default path.  Otherwise the normalised vector is written once, the Q4_K tensors share one launch
+// and every other tensor takes the launcher of its type.
+int norm_project(mg_decoder* d, int n, const uint8_t* const* w, const uint8_t* types, const float* norm_w, float* const* y,
+                 const int* rows, int cols, const char* what) {
+    int e, n4 = 0;
+    const uint8_t* w4[3];
+    float* y4[3];
+    int rows4[3];
+    for (int i = 0; i < n; ++i)
+        if (types[i] == kTypeQ4K) { w4[n4] = w[i]; y4[n4] = y[i]; rows4[n4] = rows[i]; ++n4; }
+    if (n4 == n) {
+        e = mg_rmsnorm_matvec_q4k_multi_on_stream(n, w, d->hidden, norm_w, d->cfg.rms_eps, nullptr, y, rows, cols / 256, d->stream);
+        d->mixed_launches += 1;
+        return e ? fail(d, e, what) : 0;
+    }
+    if ((e = launch_rms_norm_on_stream(d->hidden, norm_w, d->cur, 1, cols, d->cfg.rms_eps, d->stream))) return fail(d, e, "rms_norm");
+    d->mixed_launches += 1;
+    if (n4) {
+        if ((e = mg_matvec_q4k_multi_on_stream(n4, w4, d->cur, 0, nullptr, y4, rows4, cols / 256, d->stream))) return fail(d, e, what);
+        d->mixed_launches += 1;
+    }
+    for (int i = 0; i < n; ++i) {
+        if (types[i] == kTypeQ4K) continue;
+        if ((e = typed_matvec(d, types[i], w[i], d->cur, y[i], rows[i], cols))) return fail(d, e, what);
+        d->mixed_launches += 1;
+    }
+    return 0;
+}
+
+// One token of an engine whose tensors are not all of the default types (single GPU): the same
+// arithmetic, queued through the launchers of each tensor's type.  A real checkpoint mixes Q4_K with
+// Q6_K (attn_v, ffn_down, token embedding, LM head) and Q5_K.
+int queue_token_mixed(mg_decoder* d) {
+    const mg_decoder_config& c = d->cfg;
+    void* s = d->stream;
+    const int D = c.d_model, hd = c.head_dim, F = c.d_ff;
+    const int q_dim = c.n_heads * hd, kv_dim = c.n_kv_heads * hd;
+    const float scale = 1.0f / sqrtf((float)hd);
+    int e;
+    int* pos_dev = d->state;
+    int* step_dev = d->state + 2;
+    int* tok_dev = d->state + 3;
+    d->mixed_launches = 0;
+    if (d->embed_type == kTypeF16) e = mg_embed_f16_on_stream(d->embed, 0, tok_dev, d->hidden, D, c.vocab, s);
+    else e = mg_embed_kquant_on_stream(d->embed, d->embed_type, 0, tok_dev, d->hidden, D, c.vocab, s);
+    if (e) return fail(d, e, "embed");
+    d->mixed_launches += 1;
+    for (int l = 0; l < c.n_layers; ++l) {
+        const Layer& L = d->layers[l];
+        {
+            const uint8_t* w[3] = {L.wq, L.wk, L.wv};
+            float* y[3] = {d->q, d->k, d->v};
+            const int rows[3] = {q_dim, kv_dim, kv_dim};
+            if ((e = norm_project(d, 3, w, L.type, L.attn_norm, y, rows, D, "qkv"))) return e;
+        }
+        if ((e = mg_sdpa_rope_decode_f16kv_on_stream(d->q, d->k, d->v, L.k_cache, L.v_cache, d->att_full, c.n_heads,
+                                                     c.n_kv_heads, hd, 0, pos_dev, scale, c.rope_base, d->rope_freq,
+                                                     d->attn_scratch, d->n_splits, s)))
+            return fail(d, e, "attention");
+        d->mixed_launches += 1;
+        if (L.type[3] == kTypeQ4K) {   // hidden += Wo . att, added by the matvec itself
+            const uint8_t* w[1] = {L.wo};
+            float* y[1] = {d->hidden};
+            const float* add[1] = {d->hidden};
+            const int rows[1] = {D};
+            if ((e = mg_matvec_q4k_multi_on_stream(1, w, d->att_full, 0, add, y, rows, q_dim / 256, s))) return fail(d, e, "o_proj");
+            d->mixed_launches += 1;
+        } else {   // Q5_K / Q6_K: the same, the residual add folded into the matvec
+            if ((e = mg_matvec_kquant_on_stream(L.type[3], L.wo, d->att_full, 0, d->hidden, d->hidden, D, q_dim / 256, s)))
+                return fail(d, e, "o_proj");
+            d->mixed_launches += 1;
+        }
+        {
+            const uint8_t* w[2] = {L.wgate, L.wup};
+            float* y[2] = {d->gate, d->up};
+            const int rows[2] = {F, F};
+            if ((e = norm_project(d, 2, w, L.type + 4, L.ffn_norm, y, rows, D, "gate_up"))) return e;
+        }
+        if (L.type[6] == kTypeQ4K) {   // SwiGLU straight into limb records, hidden += Wdown . act in place
+            if ((e = mg_swiglu_limbs_on_stream(d->gate, d->up, nullptr, F, d->records, s))) return fail(d, e, "swiglu");
+            const uint8_t* w[1] = {L.wdown};
+            float* y[1] = {d->hidden};
+            const float* add[1] = {d->hidden};
+            const int rows[1] = {D};
+            if ((e = mg_matvec_q4k_multi_on_stream(1, w, d->records, 1, add, y, rows, F / 256, s))) return fail(d, e, "down");
+            d->mixed_launches += 2;
+        } else if (L.type[6] == kTypeQ6K && (size_t)(F / 256) * 4 * 208 <= (size_t)200 * 1024) {
+            // Q6_K takes the same limb records (while they fit one CTA's shared memory)
+            if ((e = mg_swiglu_limbs_on_stream(d->gate, d->up, nullptr, F, d->records, s))) return fail(d, e, "swiglu");
+            if ((e = mg_matvec_kquant_on_stream(kTypeQ6K, L.wdown, d->records, 1, d->hidden, d->hidden, D, F / 256, s)))
+                return fail(d, e, "down");
+            d->mixed_launches += 2;
+        } else {
+            if ((e = launch_swiglu_on_stream(d->gate, d->up, d->gate, F, s))) return fail(d, e, "swiglu");
+            if ((e = mg_matvec_kquant_on_stream(L.type[6], L.wdown, d->gate, 0, d->hidden, d->hidden, D, F / 256, s)))
+                return fail(d, e, "down");
+            d->mixed_launches += 2;
+        }
+    }
+    if ((e = launch_rms_norm_on_stream(d->hidden, d->out_norm, d->cur, 1, D, c.rms_eps, s))) return fail(d, e, "rms_norm");
+    if ((e = typed_matvec(d, d->head_type, d->lm_head, d->cur, d->logits, c.vocab, D))) return fail(d, e, "lm_head");
+    if ((e = mg_argmax_on_stream(d->logits, c.vocab, tok_dev, d->argmax_scratch, d->history, step_dev, s))) return fail(d, e, "argmax");
+    mg::launch_pdl(advance_state_kernel, dim3(1), dim3(1), 0, d->stream, d->state);
+    d->mixed_launches += 5;
     if ((e = (int)cudaGetLastError())) return fail(d, e, "advance");
     return 0;
 }
@@ -519,8 +661,14 @@ int mg_decoder_shard_ranges(const mg_decoder_config* cfg, int rank, int world, i
     return 0;
 }
 
-int mg_decoder_create_sharded(const mg_decoder_config* cfg, int rank, int world, const void* nccl_id128,
-                              mg_decoder** out) {
+}  // extern "C"
+
+namespace {
+
+// proj_types: n_layers * 7 GGUF type ids in the order wq, wk, wv, wo, wgate, wup, wdown, or null for
+// all Q4_K.
+int create_impl(const mg_decoder_config* cfg, int rank, int world, const void* nccl_id128, const int* proj_types,
+                int embed_type, int head_type, mg_decoder** out) {
     if (!cfg || !out) return (int)cudaErrorInvalidValue;
     *out = nullptr;
     const mg_decoder_config& c = *cfg;
@@ -554,6 +702,15 @@ int mg_decoder_create_sharded(const mg_decoder_config* cfg, int rank, int world,
     const int D = c.d_model, F = c.d_ff, hd = c.head_dim, q_dim = c.n_heads * hd;
     const int q_loc = (d->h1 - d->h0) * hd, kv_loc = (d->kv1 - d->kv0) * hd;
     d->layers.resize(c.n_layers);
+    d->embed_type = embed_type;
+    d->head_type = head_type;
+    d->mixed = embed_type != kTypeF16 || head_type != kTypeF16;
+    if (proj_types)
+        for (int l = 0; l < c.n_layers; ++l)
+            for (int i = 0; i < 7; ++i) {
+                d->layers[l].type[i] = (uint8_t)proj_types[l * 7 + i];
+                d->mixed = d->mixed || proj_types[l * 7 + i] != kTypeQ4K;
+            }
     {   // Every weight lives in ONE device allocation addressed by offset, as the reference's engine
         // packs its quantised tensors (crates/modgrad-gemma/src/rocm_gemma.rs:206-224); 256-byte
         // aligned sub-ranges, so every Q4_K row stays 16-byte aligned.
@@ -565,13 +722,16 @@ int mg_decoder_create_sharded(const mg_decoder_config* cfg, int rank, int world,
         };
         struct Slots { size_t wq, wk, wv, wo, wgate, wup, wdown, attn_norm, ffn_norm; };
         std::vector<Slots> slots(c.n_layers);
-        for (Slots& sl : slots) {
-            sl.wq = take(q4k_bytes(q_loc, D)); sl.wk = take(q4k_bytes(kv_loc, D)); sl.wv = take(q4k_bytes(kv_loc, D));
-            sl.wo = take(q4k_bytes(d->d_loc, q_dim)); sl.wgate = take(q4k_bytes(d->f_loc, D));
-            sl.wup = take(q4k_bytes(d->f_loc, D)); sl.wdown = take(q4k_bytes(d->d_loc, F));
+        for (int l = 0; l < c.n_layers; ++l) {
+            Slots& sl = slots[l];
+            const uint8_t* t = d->layers[l].type;
+            sl.wq = take(typed_bytes(t[0], q_loc, D)); sl.wk = take(typed_bytes(t[1], kv_loc, D));
+            sl.wv = take(typed_bytes(t[2], kv_loc, D)); sl.wo = take(typed_bytes(t[3], d->d_loc, q_dim));
+            sl.wgate = take(typed_bytes(t[4], d->f_loc, D)); sl.wup = take(typed_bytes(t[5], d->f_loc, D));
+            sl.wdown = take(typed_bytes(t[6], d->d_loc, F));
             sl.attn_norm = take((size_t)D * 4); sl.ffn_norm = take((size_t)D * 4);
         }
-        const size_t o_embed = take((size_t)c.vocab * D * 2), o_head = take((size_t)d->v_loc * D * 2),
+        const size_t o_embed = take(typed_bytes(embed_type, c.vocab, D)), o_head = take(typed_bytes(head_type, d->v_loc, D)),
                      o_norm = take((size_t)D * 4);
         if ((rc = dev_alloc(d, &d->weights, off))) return bail(rc);
         d->weights_bytes = off;
@@ -650,6 +810,31 @@ int mg_decoder_create_sharded(const mg_decoder_config* cfg, int rank, int world,
     return 0;
 }
 
+}  // namespace
+
+extern "C" {
+
+int mg_decoder_create_sharded(const mg_decoder_config* cfg, int rank, int world, const void* nccl_id128,
+                              mg_decoder** out) {
+    return create_impl(cfg, rank, world, nccl_id128, nullptr, kTypeF16, kTypeF16, out);
+}
+
+// A single-GPU engine whose tensors carry their own GGUF types, as real checkpoints mix them
+// (crates/modgrad-gemma/src/rocm_gemma.rs:291-309 dispatches per tensor the same way): every projection
+// Q4_K (12), Q5_K (13) or Q6_K (14); the token embedding and the LM head F16 (1) or one of the three.
+// proj_types holds n_layers * 7 ids in the order q, k, v, o, gate, up, down.  An engine whose types are
+// all the defaults is the one mg_decoder_create builds.
+int mg_decoder_create_typed(const mg_decoder_config* cfg, const int* proj_types, int embed_type, int head_type,
+                            mg_decoder** out) {
+    if (!cfg || !proj_types || !out) return (int)cudaErrorInvalidValue;
+    auto quant = [](int t) { return t == kTypeQ4K || t == kTypeQ5K || t == kTypeQ6K; };
+    for (int i = 0; i < cfg->n_layers * 7; ++i)
+        if (!quant(proj_types[i])) return (int)cudaErrorInvalidValue;
+    if ((embed_type != kTypeF16 && !quant(embed_type)) || (head_type != kTypeF16 && !quant(head_type)))
+        return (int)cudaErrorInvalidValue;
+    return create_impl(cfg, 0, 1, nullptr, proj_types, embed_type, head_type, out);
+}
+
 int mg_decoder_create(const mg_decoder_config* cfg, mg_decoder** out) {
     return mg_decoder_create_sharded(cfg, 0, 1, nullptr, out);
 }
@@ -667,7 +852,7 @@ void mg_decoder_destroy(mg_decoder* d) {
 
 const char* mg_decoder_last_error(const mg_decoder* d) { return d ? d->last_error.c_str() : ""; }
 
-// Uploads one tensor verbatim (Q4_K super-blocks, f32 norm weights, half embedding / LM head).
+// Uploads one tensor verbatim (the super-blocks of its type, f32 norm weights, half embedding / LM head).
 int mg_decoder_upload(mg_decoder* d, int layer, int which, const void* host, size_t bytes) {
     if (!d || !host) return (int)cudaErrorInvalidValue;
     const mg_decoder_config& c = d->cfg;
@@ -677,8 +862,8 @@ int mg_decoder_upload(mg_decoder* d, int layer, int which, const void* host, siz
     size_t want = 0;
     if (which >= MG_W_EMBED) {
         switch (which) {
-            case MG_W_EMBED: dst = d->embed; want = (size_t)c.vocab * D * 2; break;
-            case MG_W_LM_HEAD: dst = d->lm_head; want = (size_t)d->v_loc * D * 2; break;
+            case MG_W_EMBED: dst = d->embed; want = typed_bytes(d->embed_type, c.vocab, D); break;
+            case MG_W_LM_HEAD: dst = d->lm_head; want = typed_bytes(d->head_type, d->v_loc, D); break;
             case MG_W_OUT_NORM: dst = d->out_norm; want = (size_t)D * 4; break;
             default: return (int)cudaErrorInvalidValue;
         }
@@ -686,13 +871,13 @@ int mg_decoder_upload(mg_decoder* d, int layer, int which, const void* host, siz
         if (layer < 0 || layer >= c.n_layers) return (int)cudaErrorInvalidValue;
         Layer& L = d->layers[layer];
         switch (which) {
-            case MG_W_Q: dst = L.wq; want = q4k_bytes(q_loc, D); break;
-            case MG_W_K: dst = L.wk; want = q4k_bytes(kv_loc, D); break;
-            case MG_W_V: dst = L.wv; want = q4k_bytes(kv_loc, D); break;
-            case MG_W_O: dst = L.wo; want = q4k_bytes(d->d_loc, q_dim); break;
-            case MG_W_GATE: dst = L.wgate; want = q4k_bytes(d->f_loc, D); break;
-            case MG_W_UP: dst = L.wup; want = q4k_bytes(d->f_loc, D); break;
-            case MG_W_DOWN: dst = L.wdown; want = q4k_bytes(d->d_loc, F); break;
+            case MG_W_Q: dst = L.wq; want = typed_bytes(L.type[0], q_loc, D); break;
+            case MG_W_K: dst = L.wk; want = typed_bytes(L.type[1], kv_loc, D); break;
+            case MG_W_V: dst = L.wv; want = typed_bytes(L.type[2], kv_loc, D); break;
+            case MG_W_O: dst = L.wo; want = typed_bytes(L.type[3], d->d_loc, q_dim); break;
+            case MG_W_GATE: dst = L.wgate; want = typed_bytes(L.type[4], d->f_loc, D); break;
+            case MG_W_UP: dst = L.wup; want = typed_bytes(L.type[5], d->f_loc, D); break;
+            case MG_W_DOWN: dst = L.wdown; want = typed_bytes(L.type[6], d->d_loc, F); break;
             case MG_W_ATTN_NORM: dst = L.attn_norm; want = (size_t)D * 4; break;
             case MG_W_FFN_NORM: dst = L.ffn_norm; want = (size_t)D * 4; break;
             default: return (int)cudaErrorInvalidValue;
@@ -839,8 +1024,18 @@ void* mg_decoder_weight_ptr(mg_decoder* d, int layer, int which) {
         default: return nullptr;
     }
 }
+// GGUF type id of one weight tensor (the `which` codes of mg_decoder_upload); 0 (F32) for the norms, -1 on error.
+int mg_decoder_weight_type(const mg_decoder* d, int layer, int which) {
+    if (!d) return -1;
+    if (which == MG_W_EMBED) return d->embed_type;
+    if (which == MG_W_LM_HEAD) return d->head_type;
+    if (which == MG_W_OUT_NORM || which == MG_W_ATTN_NORM || which == MG_W_FFN_NORM) return 0;
+    if (layer < 0 || layer >= d->cfg.n_layers || which < MG_W_Q || which > MG_W_DOWN) return -1;
+    return d->layers[layer].type[which - MG_W_Q];
+}
 int mg_decoder_kernels_per_token(const mg_decoder* d) {
     if (!d) return 0;
+    if (d->mixed) return d->mixed_launches;  // launcher calls of the last queued token (0 before the first)
     // per layer: qkv, attention (RoPE + append + splits + merge), o, gate/up, SwiGLU, down
     if (d->world == 1) return 1 + d->cfg.n_layers * 6 + 5;
     // sharded: + the pair kernels at the end; + two residual adds per layer unless the matvecs

@@ -3,8 +3,10 @@
 //   LlmWeights::load_from_gguf        (crates/modgrad-device/src/kfd/llm.rs:233-296)
 //   RocmGemma::load                   (crates/modgrad-gemma/src/rocm_gemma.rs:94-262: VRAM guard,
 //                                      every tensor uploaded verbatim into one packed allocation)
-// for the engine in decoder.cpp: Q4_K projections, f32 norm weights, half embedding / LM head
-// (tied to the embedding when the file has no output.weight, llm.rs:1281-1286).  Tensor bytes go
+// for the engine in decoder.cpp: Q4_K / Q5_K / Q6_K projections, f32 norm weights, token embedding and
+// LM head in half or one of the three K-quants (the head tied to the embedding when the file has no
+// output.weight, llm.rs:1281-1286).  A file whose projections are all Q4_K with half embedding and
+// head gets the default engine (which also row-shards); any other mix gets the typed engine, one GPU.  Tensor bytes go
 // from the memory-mapped file straight to the device, never re-encoded; a row-sharded rank
 // uploads only its row ranges (rows are contiguous byte ranges of the row-major block array).
 #include <cuda_runtime.h>
@@ -113,8 +115,12 @@ int mg_decoder_load_gguf(const char* path, int max_seq, int rank, int world, con
     };
     std::vector<Piece> pieces;
     size_t resident = 0;
-    // rows [row0, row0 + rows) of matrix `name` ([out_dim][in_dim], dtype `want`)
-    auto add_rows = [&](const std::string& name, int layer, int which, uint32_t want, size_t in_dim, size_t out_dim,
+    enum Accept { kF32Only, kQuant, kQuantOrHalf };
+    std::vector<int> proj_types((size_t)c.n_layers * 7, (int)mggguf::kQ4_K);
+    int embed_type = (int)mggguf::kF16, head_type = (int)mggguf::kF16;
+    bool all_default = true;
+    // rows [row0, row0 + rows) of matrix `name` ([out_dim][in_dim], a tensor type that `accept` allows)
+    auto add_rows = [&](const std::string& name, int layer, int which, Accept accept, size_t in_dim, size_t out_dim,
                         size_t row0, size_t rows) -> int {
         const mggguf::TensorInfo* t = f.tensor(name);
         if (!t) return fail(-4, "missing " + name);
@@ -124,9 +130,20 @@ int mg_decoder_load_gguf(const char* path, int max_seq, int rank, int world, con
         if (in_d != in_dim || out_d != out_dim)
             return fail(-4, name + ": shape [" + std::to_string(in_d) + ", " + std::to_string(out_d) + "], expected [" +
                                 std::to_string(in_dim) + ", " + std::to_string(out_dim) + "]");
-        if (t->dtype != want)
+        const uint32_t want = t->dtype;
+        const bool quant = want == mggguf::kQ4_K || want == mggguf::kQ5_K || want == mggguf::kQ6_K;
+        const bool ok = accept == kF32Only ? want == mggguf::kF32 : (quant || (accept == kQuantOrHalf && want == mggguf::kF16));
+        if (!ok)
             return fail(-4, name + ": tensor type " + std::to_string(t->dtype) + " is not supported here (expected " +
-                                std::to_string(want) + ")");
+                                (accept == kF32Only ? "F32" : accept == kQuant ? "Q4_K, Q5_K or Q6_K" : "F16, Q4_K, Q5_K or Q6_K") +
+                                ")");
+        if (which <= MG_W_DOWN) {
+            proj_types[(size_t)layer * 7 + (which - MG_W_Q)] = (int)want;
+            all_default = all_default && want == mggguf::kQ4_K;
+        } else if (which == MG_W_EMBED || which == MG_W_LM_HEAD) {
+            (which == MG_W_EMBED ? embed_type : head_type) = (int)want;
+            all_default = all_default && want == mggguf::kF16;
+        }
         size_t bb, be;
         mggguf::block_size(want, &bb, &be);
         if (in_dim % be) return fail(-4, name + ": row length is not a whole number of blocks");
@@ -139,20 +156,23 @@ int mg_decoder_load_gguf(const char* path, int max_seq, int rank, int world, con
     };
     for (int l = 0; l < c.n_layers; ++l) {
         const std::string p = "blk." + std::to_string(l) + ".";
-        if ((rc = add_rows(p + "attn_q.weight", l, MG_W_Q, mggguf::kQ4_K, D, q_dim, (size_t)h0 * hd, (size_t)(h1 - h0) * hd))) return rc;
-        if ((rc = add_rows(p + "attn_k.weight", l, MG_W_K, mggguf::kQ4_K, D, kv_dim, (size_t)kv0 * hd, (size_t)(kv1 - kv0) * hd))) return rc;
-        if ((rc = add_rows(p + "attn_v.weight", l, MG_W_V, mggguf::kQ4_K, D, kv_dim, (size_t)kv0 * hd, (size_t)(kv1 - kv0) * hd))) return rc;
-        if ((rc = add_rows(p + "attn_output.weight", l, MG_W_O, mggguf::kQ4_K, q_dim, D, (size_t)rank * d_loc, d_loc))) return rc;
-        if ((rc = add_rows(p + "ffn_gate.weight", l, MG_W_GATE, mggguf::kQ4_K, D, F, (size_t)rank * f_loc, f_loc))) return rc;
-        if ((rc = add_rows(p + "ffn_up.weight", l, MG_W_UP, mggguf::kQ4_K, D, F, (size_t)rank * f_loc, f_loc))) return rc;
-        if ((rc = add_rows(p + "ffn_down.weight", l, MG_W_DOWN, mggguf::kQ4_K, F, D, (size_t)rank * d_loc, d_loc))) return rc;
-        if ((rc = add_rows(p + "attn_norm.weight", l, MG_W_ATTN_NORM, mggguf::kF32, D, 1, 0, 1))) return rc;
-        if ((rc = add_rows(p + "ffn_norm.weight", l, MG_W_FFN_NORM, mggguf::kF32, D, 1, 0, 1))) return rc;
+        if ((rc = add_rows(p + "attn_q.weight", l, MG_W_Q, kQuant, D, q_dim, (size_t)h0 * hd, (size_t)(h1 - h0) * hd))) return rc;
+        if ((rc = add_rows(p + "attn_k.weight", l, MG_W_K, kQuant, D, kv_dim, (size_t)kv0 * hd, (size_t)(kv1 - kv0) * hd))) return rc;
+        if ((rc = add_rows(p + "attn_v.weight", l, MG_W_V, kQuant, D, kv_dim, (size_t)kv0 * hd, (size_t)(kv1 - kv0) * hd))) return rc;
+        if ((rc = add_rows(p + "attn_output.weight", l, MG_W_O, kQuant, q_dim, D, (size_t)rank * d_loc, d_loc))) return rc;
+        if ((rc = add_rows(p + "ffn_gate.weight", l, MG_W_GATE, kQuant, D, F, (size_t)rank * f_loc, f_loc))) return rc;
+        if ((rc = add_rows(p + "ffn_up.weight", l, MG_W_UP, kQuant, D, F, (size_t)rank * f_loc, f_loc))) return rc;
+        if ((rc = add_rows(p + "ffn_down.weight", l, MG_W_DOWN, kQuant, F, D, (size_t)rank * d_loc, d_loc))) return rc;
+        if ((rc = add_rows(p + "attn_norm.weight", l, MG_W_ATTN_NORM, kF32Only, D, 1, 0, 1))) return rc;
+        if ((rc = add_rows(p + "ffn_norm.weight", l, MG_W_FFN_NORM, kF32Only, D, 1, 0, 1))) return rc;
     }
-    if ((rc = add_rows("token_embd.weight", 0, MG_W_EMBED, mggguf::kF16, D, c.vocab, 0, c.vocab))) return rc;
+    if ((rc = add_rows("token_embd.weight", 0, MG_W_EMBED, kQuantOrHalf, D, c.vocab, 0, c.vocab))) return rc;
     const char* head = f.tensor("output.weight") ? "output.weight" : "token_embd.weight";  // tied when absent
-    if ((rc = add_rows(head, 0, MG_W_LM_HEAD, mggguf::kF16, D, c.vocab, (size_t)rank * v_loc, v_loc))) return rc;
-    if ((rc = add_rows("output_norm.weight", 0, MG_W_OUT_NORM, mggguf::kF32, D, 1, 0, 1))) return rc;
+    if ((rc = add_rows(head, 0, MG_W_LM_HEAD, kQuantOrHalf, D, c.vocab, (size_t)rank * v_loc, v_loc))) return rc;
+    if ((rc = add_rows("output_norm.weight", 0, MG_W_OUT_NORM, kF32Only, D, 1, 0, 1))) return rc;
+
+    if (!all_default && world != 1)
+        return fail(-4, "row sharding needs Q4_K projections with a half embedding and LM head; this file mixes other tensor types");
 
     // VRAM guard (rocm_gemma.rs:110-138): weights + KV cache + activations must fit with headroom.
     resident += (size_t)c.n_layers * 2 * (size_t)max_seq * (kv1 - kv0) * hd * 2;  // half K and V
@@ -170,7 +190,8 @@ int mg_decoder_load_gguf(const char* path, int max_seq, int rank, int world, con
     }
 
     mg_decoder* d = nullptr;
-    rc = mg_decoder_create_sharded(&c, rank, world, nccl_id128, &d);
+    rc = all_default ? mg_decoder_create_sharded(&c, rank, world, nccl_id128, &d)
+                     : mg_decoder_create_typed(&c, proj_types.data(), embed_type, head_type, &d);
     if (rc) return fail(rc, std::string("mg_decoder_create: ") + cudaGetErrorString((cudaError_t)rc));
     for (const Piece& pc : pieces) {
         rc = mg_decoder_upload(d, pc.layer, pc.which, pc.src, pc.bytes);

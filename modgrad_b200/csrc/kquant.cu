@@ -16,14 +16,17 @@
 //        (nibble (k >= 2) of ql[64G + 32(k&1) + l] | bits 2k,2k+1 of qh[32G + l] << 4) - 32, scale
 //        sc[8G + 2k + l/16];  w = fl(fl(d*sc) * q).  Rows are only 2-byte aligned (210 = 2 * 105).
 //
-// Kernel shape (both formats): one warp per row, lane l owns byte column l of every quant group, so
-// every load instruction of the warp covers 32 consecutive bytes (or 128 bytes of x); eight weights
-// per lane and super-block, f32 accumulate, warp-shuffle reduction.  HBM-bound work done with byte
-// loads: correct and coalesced, not yet tuned like the Q4_K kernels.
+// Matvec kernel shape (both formats): a CTA owns a few consecutive rows and its warps split the rows'
+// super-blocks, one block per warp and step; a lane owns adjacent columns of every quant group (packed
+// 32-bit loads for Q5_K, 16-bit for the 2-byte-aligned Q6_K), eight weights per lane and block, f32
+// accumulate, warp-shuffle then fixed-order cross-warp reduction.  The dequantisers keep one warp per
+// block with byte loads.
 #include <float.h>
 
+#include "gemv_q4k_device.cuh"
 #include "launch_common.cuh"
 #include "q4k_device.cuh"
+#include "xlimbs.cuh"
 
 namespace {
 
@@ -100,45 +103,369 @@ __global__ void __launch_bounds__(kThreads) dequant_q6k_kernel(const uint8_t* __
     }
 }
 
-// kind 5 / 6; x is read after the previous kernel of the stream has completed.
+// One row of a quantised token-embedding table, dequantised exactly as the bulk dequantisers do
+// (the reference dequantises the row on the host and uploads it: crates/modgrad-gemma/src/rocm_gemma.rs:316-323).
+// The token is a device-side integer, so the launch can sit in a replayed graph.  One warp per super-block.
 template <int KIND>
-__global__ void __launch_bounds__(kThreads) matvec_kquant_kernel(const uint8_t* __restrict__ w, const float* x, float* y,
-                                                                 int out_dim, int bpr) {
+__global__ void __launch_bounds__(kThreads) embed_kquant_kernel(const uint8_t* __restrict__ table, const int* token_dev,
+                                                                int token_arg, float* __restrict__ out, int bpr,
+                                                                int vocab) {
     mg::pdl_prologue();
+    int tok = token_dev ? *token_dev : token_arg;
+    tok = min(max(tok, 0), vocab - 1);
     const int lane = threadIdx.x & 31;
+    const int blk = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    if (blk >= bpr) return;
+    constexpr int kBytes = KIND == 4 ? 144 : KIND == 5 ? kQ5Bytes : kQ6Bytes;
+    const uint8_t* b = table + ((size_t)tok * bpr + blk) * kBytes;
+    float* o = out + (size_t)blk * 256;
+    if (KIND == 4) {
+        const uint4 h = *reinterpret_cast<const uint4*>(b);
+        const float d = q4k::half_bits_finite_or_zero(h.x);
+        const float dmin = q4k::half_bits_finite_or_zero(h.x >> 16);
+        const q4k::ScaleMin sm = q4k::unpack_scales(h.y, h.z, h.w);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const uint32_t v = b[16 + 32 * g + lane];
+            const float d_lo = __fmul_rn(d, (float)q4k::scale_of(sm, 2 * g)), m_lo = __fmul_rn(dmin, (float)q4k::min_of(sm, 2 * g));
+            const float d_hi = __fmul_rn(d, (float)q4k::scale_of(sm, 2 * g + 1)),
+                        m_hi = __fmul_rn(dmin, (float)q4k::min_of(sm, 2 * g + 1));
+            o[64 * g + lane] = __fsub_rn(__fmul_rn(d_lo, (float)(v & 0xFu)), m_lo);
+            o[64 * g + 32 + lane] = __fsub_rn(__fmul_rn(d_hi, (float)(v >> 4)), m_hi);
+        }
+    } else if (KIND == 5) {
+        const Q5Header h = q5_header(b);
+        const uint32_t qh = b[16 + lane];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const uint32_t v = b[48 + 32 * g + lane];
+            const float q_lo = (float)((v & 0xFu) + (((qh >> (2 * g)) & 1u) << 4));
+            const float q_hi = (float)((v >> 4) + (((qh >> (2 * g + 1)) & 1u) << 4));
+            o[64 * g + lane] = __fsub_rn(__fmul_rn(h.dsc[2 * g], q_lo), h.dm[2 * g]);
+            o[64 * g + 32 + lane] = __fsub_rn(__fmul_rn(h.dsc[2 * g + 1], q_hi), h.dm[2 * g + 1]);
+        }
+    } else {
+        const float d = q6_d(b);
+        const int8_t* sc = reinterpret_cast<const int8_t*>(b + 192);
+#pragma unroll
+        for (int G = 0; G < 2; ++G) {
+            int qv[4];
+            q6_quants(b, G, lane, qv);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                o[128 * G + 32 * k + lane] = __fmul_rn(__fmul_rn(d, (float)sc[8 * G + 2 * k + (lane >> 4)]), (float)qv[k]);
+        }
+    }
+}
+
+// The float 2^23 + b for byte I of `packed` (one byte permute): subtracting 2^23 (+ an offset) is exact.
+template <int I>
+__device__ __forceinline__ float byte_as_f(uint32_t packed) {
+    return __uint_as_float(__byte_perm(packed, 0x4B000000u, 0x7540 + I));
+}
+__device__ __forceinline__ float2 ld_x2(const float* p, bool aligned) {
+    return aligned ? *reinterpret_cast<const float2*>(p) : make_float2(p[0], p[1]);
+}
+__device__ __forceinline__ float4 ld_x4(const float* p, bool aligned) {
+    return aligned ? *reinterpret_cast<const float4*>(p) : make_float4(p[0], p[1], p[2], p[3]);
+}
+
+// kind 5 / 6; x is read after the previous kernel of the stream has completed.
+// A CTA of WARPS warps owns R consecutive rows at a time; its warps split the rows' super-blocks among
+// them (warp w takes blocks w, w + WARPS, ...), so a long row is read by many loads in flight instead of
+// one warp's serial walk, and every activation load serves R rows.  Within a block a lane owns a few
+// adjacent columns of every quant group, extracts them four (Q5_K) or two (Q6_K) at a time from packed
+// words, and applies each sub-block's scale once per group of columns, not once per weight.
+template <int KIND, int R, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) matvec_kquant_kernel(const uint8_t* __restrict__ w, const float* x,
+                                                                   const float* add, float* y, int out_dim, int bpr,
+                                                                   int x_aligned) {
+    mg::pdl_prologue();
+    __shared__ float part[WARPS][R];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int kBytes = KIND == 5 ? kQ5Bytes : kQ6Bytes;
-    for (int row = blockIdx.x * kWarps + (threadIdx.x >> 5); row < out_dim; row += gridDim.x * kWarps) {
-        const uint8_t* wr = w + (size_t)row * bpr * kBytes;
-        float acc = 0.0f;
-        for (int blk = 0; blk < bpr; ++blk) {
-            const uint8_t* b = wr + (size_t)blk * kBytes;
+    const bool xa = x_aligned != 0;
+    for (int row0 = blockIdx.x * R; row0 < out_dim; row0 += gridDim.x * R) {
+        float acc[R];
+        const uint8_t* wr[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            acc[r] = 0.0f;
+            wr[r] = w + (size_t)min(row0 + r, out_dim - 1) * bpr * kBytes;  // a row past the end repeats the last one
+        }
+        for (int blk = warp; blk < bpr; blk += WARPS) {
             const float* xb = x + (size_t)blk * 256;
             if (KIND == 5) {
-                const Q5Header h = q5_header(b);
-                const uint32_t qh = b[16 + lane];
+                // lane: quant group g (64 columns), columns 4j..4j+3 of its low and of its high nibble half
+                const int g = lane >> 3, j = lane & 7;
+                const float4 xl = ld_x4(xb + 64 * g + 4 * j, xa), xh = ld_x4(xb + 64 * g + 32 + 4 * j, xa);
+                const float sxl = (xl.x + xl.y) + (xl.z + xl.w), sxh = (xh.x + xh.y) + (xh.z + xh.w);
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const uint32_t v = b[48 + 32 * g + lane];
-                    const float q_lo = (float)((v & 0xFu) + (((qh >> (2 * g)) & 1u) << 4));
-                    const float q_hi = (float)((v >> 4) + (((qh >> (2 * g + 1)) & 1u) << 4));
-                    acc = fmaf(fmaf(h.dsc[2 * g], q_lo, -h.dm[2 * g]), xb[64 * g + lane], acc);
-                    acc = fmaf(fmaf(h.dsc[2 * g + 1], q_hi, -h.dm[2 * g + 1]), xb[64 * g + 32 + lane], acc);
+                for (int r = 0; r < R; ++r) {
+                    const uint8_t* b = wr[r] + (size_t)blk * kQ5Bytes;
+                    const uint4 h = q4k::ld_nc_u4(b);
+                    const uint32_t v = *reinterpret_cast<const uint32_t*>(b + 48 + 32 * g + 4 * j);
+                    const uint32_t qh = *reinterpret_cast<const uint32_t*>(b + 16 + 4 * j);
+                    const float d = q4k::half_bits_finite_or_zero(h.x), dmin = q4k::half_bits_finite_or_zero(h.x >> 16);
+                    const q4k::ScaleMin sm = q4k::unpack_scales(h.y, h.z, h.w);
+                    const uint32_t ql = (v & 0x0F0F0F0Fu) | (((qh >> (2 * g)) & 0x01010101u) << 4);
+                    const uint32_t qu = ((v >> 4) & 0x0F0F0F0Fu) | (((qh >> (2 * g + 1)) & 0x01010101u) << 4);
+                    constexpr float k23 = 8388608.0f;
+                    float tl = (byte_as_f<0>(ql) - k23) * xl.x, tu = (byte_as_f<0>(qu) - k23) * xh.x;
+                    tl = fmaf(byte_as_f<1>(ql) - k23, xl.y, tl); tu = fmaf(byte_as_f<1>(qu) - k23, xh.y, tu);
+                    tl = fmaf(byte_as_f<2>(ql) - k23, xl.z, tl); tu = fmaf(byte_as_f<2>(qu) - k23, xh.z, tu);
+                    tl = fmaf(byte_as_f<3>(ql) - k23, xl.w, tl); tu = fmaf(byte_as_f<3>(qu) - k23, xh.w, tu);
+                    const float dl = d * (float)q4k::scale_of(sm, 2 * g), du = d * (float)q4k::scale_of(sm, 2 * g + 1);
+                    const float ml = dmin * (float)q4k::min_of(sm, 2 * g), mu = dmin * (float)q4k::min_of(sm, 2 * g + 1);
+                    acc[r] += fmaf(dl, tl, -ml * sxl) + fmaf(du, tu, -mu * sxh);
                 }
             } else {
-                const float d = q6_d(b);
-                const int8_t* sc = reinterpret_cast<const int8_t*>(b + 192);
+                // lane: half G of the block (128 columns), columns 2j, 2j+1 of each of its four 32-column groups
+                // (Q6_K blocks are only 2-byte aligned: 16-bit loads)
+                const int G = lane >> 4, j = lane & 15;
+                const float* xg = xb + 128 * G + 2 * j;
+                const float2 x0 = ld_x2(xg, xa), x1 = ld_x2(xg + 32, xa), x2 = ld_x2(xg + 64, xa), x3 = ld_x2(xg + 96, xa);
 #pragma unroll
-                for (int G = 0; G < 2; ++G) {
-                    int qv[4];
-                    q6_quants(b, G, lane, qv);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        acc = fmaf(d * (float)sc[8 * G + 2 * k + (lane >> 4)] * (float)qv[k], xb[128 * G + 32 * k + lane], acc);
+                for (int r = 0; r < R; ++r) {
+                    const uint8_t* b = wr[r] + (size_t)blk * kQ6Bytes;
+                    const uint32_t a = *reinterpret_cast<const uint16_t*>(b + 64 * G + 2 * j);
+                    const uint32_t c = *reinterpret_cast<const uint16_t*>(b + 64 * G + 32 + 2 * j);
+                    const uint32_t h = *reinterpret_cast<const uint16_t*>(b + 128 + 32 * G + 2 * j);
+                    const uint8_t* sc = b + 192 + 8 * G + (j >> 3);   // scales of groups k = 0..3 at sc[2k], as signed bytes
+                    const float d = q4k::half_bits_finite_or_zero(*reinterpret_cast<const uint16_t*>(b + 208));
+                    const uint32_t q0 = (a & 0x0F0Fu) | ((h & 0x0303u) << 4), q1 = (c & 0x0F0Fu) | (((h >> 2) & 0x0303u) << 4);
+                    const uint32_t q2 = ((a >> 4) & 0x0F0Fu) | (((h >> 4) & 0x0303u) << 4),
+                                   q3 = ((c >> 4) & 0x0F0Fu) | (((h >> 6) & 0x0303u) << 4);
+                    constexpr float kq = 8388608.0f + 32.0f;     // quants are stored with +32
+                    constexpr float ks = 8388608.0f + 128.0f;    // signed scale byte ^ 0x80 = scale + 128
+                    const float t0 = fmaf(byte_as_f<1>(q0) - kq, x0.y, (byte_as_f<0>(q0) - kq) * x0.x);
+                    const float t1 = fmaf(byte_as_f<1>(q1) - kq, x1.y, (byte_as_f<0>(q1) - kq) * x1.x);
+                    const float t2 = fmaf(byte_as_f<1>(q2) - kq, x2.y, (byte_as_f<0>(q2) - kq) * x2.x);
+                    const float t3 = fmaf(byte_as_f<1>(q3) - kq, x3.y, (byte_as_f<0>(q3) - kq) * x3.x);
+                    const float s0 = byte_as_f<0>((uint32_t)sc[0] ^ 0x80u) - ks, s1 = byte_as_f<0>((uint32_t)sc[2] ^ 0x80u) - ks;
+                    const float s2 = byte_as_f<0>((uint32_t)sc[4] ^ 0x80u) - ks, s3 = byte_as_f<0>((uint32_t)sc[6] ^ 0x80u) - ks;
+                    acc[r] = fmaf(d, fmaf(s0, t0, s1 * t1) + fmaf(s2, t2, s3 * t3), acc[r]);
                 }
             }
         }
-        acc = q4k::warp_sum(acc);
-        if (lane == 0) y[row] = acc;
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[r] = q4k::warp_sum(acc[r]);
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) part[warp][r] = acc[r];
+        }
+        __syncthreads();
+        if (threadIdx.x < R && row0 + threadIdx.x < out_dim) {
+            float t = 0.0f;
+#pragma unroll
+            for (int wv = 0; wv < WARPS; ++wv) t += part[wv][threadIdx.x];   // fixed order: the same sum on every run
+            y[row0 + threadIdx.x] = add ? add[row0 + threadIdx.x] + t : t;
+        }
+        __syncthreads();
+    }
+}
+
+// ---- Q6_K on limb records -------------------------------------------------------------------------
+// The float kernel above spends about 12 lane-operations per weight (a byte permute, a subtraction
+// and a multiply-add for each, plus the extraction) and is bound by instruction issue at a quarter of
+// the memory bandwidth.  This kernel multiplies the 6-bit quants with the activations in integers, as
+// the Q4_K kernels do (xlimbs.cuh): the activations are three byte limbs sharing one power-of-two
+// scale per 32 elements, the quants are sign-extended bytes, and eight weights meet their
+// activations in six dp4a.  The integer sums are exact; the result differs from the float kernel's by
+// the rounding of the activations to 23 bits of their sub-block's largest element.
+//
+// A lane owns eight adjacent columns (qtr) of all four 32-column groups of one half (G) of a block:
+// 32 weights from six packed words, each group with its own scale byte and its own activation
+// sub-block.  Eight lanes cover a block, a warp four blocks per step and R rows at a time; every CTA
+// keeps the whole activation vector as limb records in shared memory.
+__device__ __forceinline__ int dp4a_su(uint32_t a_signed, uint32_t b_unsigned, int c) {
+    int d;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_signed), "r"(b_unsigned), "r"(c));
+    return d;
+}
+// Eight bytes from a 2-byte-aligned address inside a 4-byte-aligned array: three aligned words
+// funnel-shifted.  Reads up to 2 bytes before and 6 bytes after the eight.
+__device__ __forceinline__ uint2 ld8_align2(const uint8_t* p) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(a & ~(uintptr_t)3);
+    const uint32_t sh = (uint32_t)(a & 2u) * 8u;
+    const uint32_t w0 = __ldg(q), w1 = __ldg(q + 1), w2 = __ldg(q + 2);
+    return make_uint2(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh));
+}
+// Four 6-bit quants (stored + 32) of group K as sign-extended bytes: nibbles of ql word `lo`,
+// bits 2K, 2K+1 of every byte of qh word `h`.
+template <int K>
+__device__ __forceinline__ uint32_t q6_signed4(uint32_t lo, uint32_t h) {
+    const uint32_t u = (K >= 2 ? lo >> 4 : lo) & 0x0F0F0F0Fu;
+    const uint32_t hs = K == 0 ? h << 4 : K == 1 ? h << 2 : K == 2 ? h : h >> 2;
+    const uint32_t q = u | (hs & 0x30303030u);            // 0..63
+    const uint32_t neg = ~q & 0x20202020u;                // below 32: negative once 32 is taken off
+    return (q ^ 0x20202020u) + neg * 6u;                  // bit 5 flipped, bits 6 and 7 set where negative
+}
+
+// R rows' dot products with one block of activations: acc[r] += d_r * sum_k sc_rk * s_k * <q_rk, a_k> for the
+// 32 weights of lane (G, qtr).  wr[r]: row r; rec_w: the records of the whole vector.
+template <int R>
+__device__ __forceinline__ void q6_block_dot(const uint8_t* const (&wr)[R], const uint32_t* rec_w, int blk, int G, int qtr,
+                                             float (&acc)[R]) {
+    uint2 ql0[R], ql1[R], qh[R];
+    int sc[R][4];
+    float d[R], part[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const uint8_t* b = wr[r] + (size_t)blk * kQ6Bytes;
+        ql0[r] = ld8_align2(b + 64 * G + 8 * qtr);
+        ql1[r] = ld8_align2(b + 64 * G + 32 + 8 * qtr);
+        qh[r] = ld8_align2(b + 128 + 32 * G + 8 * qtr);
+        const int8_t* s8 = reinterpret_cast<const int8_t*>(b + 192 + 8 * G + (qtr >> 1));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) sc[r][k] = (int)s8[2 * k];
+        d[r] = q4k::half_bits_finite_or_zero(*reinterpret_cast<const uint16_t*>(b + 208));
+        part[r] = 0.0f;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        // activations of sub-block 4G + k: record 2G + k/2, low or high plane set, words 2qtr, 2qtr + 1
+        const uint32_t* rp = rec_w + (size_t)(blk * 4 + 2 * G + (k >> 1)) * xlimbs::kRecordWords;
+        const uint32_t* lp = rp + (k & 1) * 24 + 2 * qtr;
+        const uint2 a2 = *reinterpret_cast<const uint2*>(lp);
+        const uint2 a1 = *reinterpret_cast<const uint2*>(lp + 8);
+        const uint2 a0 = *reinterpret_cast<const uint2*>(lp + 16);
+        const float s = __uint_as_float(rp[48 + (k & 1)]);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const uint2 lo = (k & 1) ? ql1[r] : ql0[r];
+            uint32_t qa, qb;
+            if (k == 0) { qa = q6_signed4<0>(lo.x, qh[r].x); qb = q6_signed4<0>(lo.y, qh[r].y); }
+            else if (k == 1) { qa = q6_signed4<1>(lo.x, qh[r].x); qb = q6_signed4<1>(lo.y, qh[r].y); }
+            else if (k == 2) { qa = q6_signed4<2>(lo.x, qh[r].x); qb = q6_signed4<2>(lo.y, qh[r].y); }
+            else { qa = q6_signed4<3>(lo.x, qh[r].x); qb = q6_signed4<3>(lo.y, qh[r].y); }
+            const int i2 = gemvdev::dp4a_ss(qb, a2.y, gemvdev::dp4a_ss(qa, a2.x, 0));
+            const int i1 = dp4a_su(qb, a1.y, dp4a_su(qa, a1.x, 0));
+            const int i0 = dp4a_su(qb, a0.y, dp4a_su(qa, a0.x, 0));
+            // |i2| <= 2^15, |i1 * 256 + i0| < 2^24: both conversions are exact
+            const float f = fmaf((float)i2, 65536.0f, (float)(i1 * 256 + i0));
+            part[r] = fmaf(f * s, (float)sc[r][k], part[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = fmaf(d[r], part[r], acc[r]);
+}
+
+// The activation vector as limb records in shared memory.  FROM_X = 1: src is the f32 vector, converted
+// here; 0: src holds records (mg_q4k_x_to_limbs_on_stream, mg_swiglu_limbs_on_stream).
+template <int FROM_X, int THREADS>
+__device__ __forceinline__ void q6_stage_records(const void* src, int bpr, int x_aligned, uint4* rec_s) {
+    if (FROM_X) {
+        const float* x = static_cast<const float*>(src);
+        const int n_chunks = bpr * 64;   // a multiple of 64: warps are whole
+        for (int c = threadIdx.x; c < n_chunks; c += THREADS) {
+            float v[4];
+            gemvdev::load_chunk<false>(v, x, c, x_aligned);
+            gemvdev::convert_chunk(v, c, reinterpret_cast<uint32_t*>(rec_s));
+        }
+    } else {
+        const uint4* rec_g = static_cast<const uint4*>(src);
+        const int n_vec = bpr * 4 * xlimbs::kRecordVec4;
+        for (int i = threadIdx.x; i < n_vec; i += THREADS) gemvdev::cp_async16(&rec_s[i], &rec_g[i]);
+        gemvdev::cp_async_wait_all();
+    }
+    __syncthreads();
+}
+
+constexpr int kQ6LimbThreads = 256, kQ6LimbWarps = kQ6LimbThreads / 32;
+
+// Short rows, many of them: a warp owns R rows at a time and walks their blocks four per step.
+// y[row] = (add ? add[row] : 0) + W[row] . x.
+template <int R, int FROM_X>
+__global__ void __launch_bounds__(kQ6LimbThreads) matvec_q6k_limbs_kernel(const uint8_t* __restrict__ w, const void* src,
+                                                                          const float* add, float* y, int out_dim, int bpr,
+                                                                          int x_aligned) {
+    extern __shared__ __align__(16) uint4 rec_s[];
+    const uint32_t* rec_w = reinterpret_cast<const uint32_t*>(rec_s);
+    mg::pdl_prologue();
+    q6_stage_records<FROM_X, kQ6LimbThreads>(src, bpr, x_aligned, rec_s);
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int bsel = lane >> 3, G = (lane >> 2) & 1, qtr = lane & 3;
+    const size_t row_bytes = (size_t)bpr * kQ6Bytes;
+    for (int row0 = (blockIdx.x * kQ6LimbWarps + warp) * R; row0 < out_dim; row0 += gridDim.x * kQ6LimbWarps * R) {
+        float acc[R];
+        const uint8_t* wr[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            acc[r] = 0.0f;
+            wr[r] = w + (size_t)min(row0 + r, out_dim - 1) * row_bytes;   // a row past the end repeats the last one
+        }
+        for (int blk = bsel; blk < bpr; blk += 4) q6_block_dot<R>(wr, rec_w, blk, G, qtr, acc);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float t = q4k::warp_sum(acc[r]);
+            if (lane == 0 && row0 + r < out_dim) y[row0 + r] = add ? add[row0 + r] + t : t;
+        }
+    }
+}
+
+// Long rows, few of them (a down projection): one CTA per SM keeps the records (one copy per SM, not
+// per small CTA) and takes an even share of the rows; its 96 eight-lane groups walk the (row, block)
+// pairs of up to 32 rows cyclically, so that every group has the same number of blocks whatever the
+// row length, and leave one partial sum per (row, group) in shared memory, summed in a fixed order.
+constexpr int kQ6LongThreads = 768, kQ6LongGroups = kQ6LongThreads / 8, kQ6LongRows = 32;
+
+template <int FROM_X>
+__global__ void __launch_bounds__(kQ6LongThreads, 1) matvec_q6k_limbs_long_kernel(const uint8_t* __restrict__ w, const void* src,
+                                                                                  const float* add, float* y, int out_dim,
+                                                                                  int bpr, int x_aligned) {
+    extern __shared__ __align__(16) uint4 rec_s[];
+    const uint32_t* rec_w = reinterpret_cast<const uint32_t*>(rec_s);
+    float* part = reinterpret_cast<float*>(rec_s + (size_t)bpr * 4 * xlimbs::kRecordVec4);   // [kQ6LongRows][kQ6LongGroups]
+    mg::pdl_prologue();
+    q6_stage_records<FROM_X, kQ6LongThreads>(src, bpr, x_aligned, rec_s);
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int group = threadIdx.x >> 3, G = (lane >> 2) & 1, qtr = lane & 3;
+    const unsigned gmask = 0xFFu << (lane & 24);   // the eight lanes of this group
+    const size_t row_bytes = (size_t)bpr * kQ6Bytes;
+    const int row_begin = (int)((long long)blockIdx.x * out_dim / gridDim.x);
+    const int row_end = (int)((long long)(blockIdx.x + 1) * out_dim / gridDim.x);
+    for (int pass0 = row_begin; pass0 < row_end; pass0 += kQ6LongRows) {
+        const int n_rows = min(kQ6LongRows, row_end - pass0);
+        for (int i = threadIdx.x; i < kQ6LongRows * kQ6LongGroups; i += kQ6LongThreads) part[i] = 0.0f;
+        __syncthreads();
+        const int n_items = n_rows * bpr;
+        int cur = -1;
+        float acc[1] = {0.0f};
+        for (int j = group; j < n_items; j += kQ6LongGroups) {
+            const int rl = j / bpr, blk = j - rl * bpr;
+            if (rl != cur) {   // the whole group moves on together
+                if (cur >= 0) {
+                    float v = acc[0];
+                    v += __shfl_xor_sync(gmask, v, 4);
+                    v += __shfl_xor_sync(gmask, v, 2);
+                    v += __shfl_xor_sync(gmask, v, 1);
+                    if ((lane & 7) == 0) part[cur * kQ6LongGroups + group] = v;
+                }
+                cur = rl;
+                acc[0] = 0.0f;
+            }
+            const uint8_t* wr[1] = {w + (size_t)(pass0 + rl) * row_bytes};
+            q6_block_dot<1>(wr, rec_w, blk, G, qtr, acc);
+        }
+        if (cur >= 0) {
+            float v = acc[0];
+            v += __shfl_xor_sync(gmask, v, 4);
+            v += __shfl_xor_sync(gmask, v, 2);
+            v += __shfl_xor_sync(gmask, v, 1);
+            if ((lane & 7) == 0) part[cur * kQ6LongGroups + group] = v;
+        }
+        __syncthreads();
+        for (int rl = warp; rl < n_rows; rl += kQ6LongThreads / 32) {
+            const float* pr = part + rl * kQ6LongGroups;
+            float t = (pr[lane] + pr[32 + lane]) + pr[64 + lane];
+            t = q4k::warp_sum(t);
+            if (lane == 0) y[pass0 + rl] = add ? add[pass0 + rl] + t : t;
+        }
+        __syncthreads();   // before the partial sums are cleared for the next rows
     }
 }
 
@@ -181,14 +508,84 @@ int grid_for(int work_items) {
     return grid < 1 ? 1 : grid;
 }
 
+template <int KIND, int R, int WARPS>
+int launch_matvec_shape(const uint8_t* w, const float* x, const float* add, float* y, int out_dim, int bpr, void* stream) {
+    const mg::DeviceProps& dp = mg::device_props();
+    const int sms = dp.ok ? dp.sm_count : 148;
+    int grid = (out_dim + R - 1) / R;
+    const int resident = sms * (2048 / (WARPS * 32));
+    if (grid > resident) grid = resident;
+    return (int)mg::launch_pdl(matvec_kquant_kernel<KIND, R, WARPS>, dim3((unsigned)grid), dim3(WARPS * 32), 0,
+                               (cudaStream_t)stream, w, x, add, y, out_dim, bpr, mg::aligned16(x) ? 1 : 0);
+}
+
 template <int KIND>
-int launch_matvec(const uint8_t* w, const float* x, float* y, int out_dim, int bpr, void* stream) {
-    if (out_dim <= 0 || bpr <= 0) return (int)cudaErrorInvalidValue;
-    if (!w || !x || !y) return (int)cudaErrorInvalidValue;
-    if (KIND == 5 && !mg::aligned16(w)) return (int)cudaErrorInvalidValue;
+int launch_matvec(const uint8_t* w, const float* x, const float* add, float* y, int out_dim, int bpr, void* stream) {
+    // long rows: eight warps share two rows; short rows: four warps share four
+    if (bpr >= 32) return launch_matvec_shape<KIND, 2, 8>(w, x, add, y, out_dim, bpr, stream);
+    return launch_matvec_shape<KIND, 4, 4>(w, x, add, y, out_dim, bpr, stream);
+}
+
+// Rows longer than this take the kernel that splits a row's blocks over a whole CTA.
+constexpr int kQ6LongMinBpr = 33;
+
+// The limb kernels need the weight 4-byte aligned (their 8-byte loads round the address down) and the
+// whole activation vector as records in one CTA's shared memory.
+size_t q6_smem_bytes(int bpr) {
+    return (size_t)bpr * 4 * xlimbs::kRecordBytes +
+           (bpr >= kQ6LongMinBpr ? (size_t)kQ6LongRows * kQ6LongGroups * sizeof(float) : 0);
+}
+bool q6_limbs_ok(const uint8_t* w, int bpr) {
+    const mg::DeviceProps& dp = mg::device_props();
+    return (reinterpret_cast<uintptr_t>(w) & 3u) == 0 && dp.ok && q6_smem_bytes(bpr) <= (size_t)dp.max_smem_optin;
+}
+
+template <class Kernel>
+int q6_allow_smem(Kernel kernel, size_t smem, size_t& configured) {
+    if (smem <= 48 * 1024 || smem <= configured) return 0;
+    const mg::DeviceProps& dp = mg::device_props();
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.max_smem_optin);
+    if (e != cudaSuccess) return (int)e;
+    configured = (size_t)dp.max_smem_optin;
+    return 0;
+}
+
+template <int FROM_X>
+int launch_q6_limbs(const uint8_t* w, const void* src, const float* add, float* y, int out_dim, int bpr, void* stream) {
+    const mg::DeviceProps& dp = mg::device_props();
+    const size_t smem = q6_smem_bytes(bpr);
+    const int x_aligned = mg::aligned16(src) ? 1 : 0;
+    if (bpr >= kQ6LongMinBpr) {
+        static size_t configured = 0;   // the largest dynamic shared memory the kernel was configured for
+        if (int rc = q6_allow_smem(matvec_q6k_limbs_long_kernel<FROM_X>, smem, configured)) return rc;
+        const int grid = out_dim < dp.sm_count ? out_dim : dp.sm_count;
+        return (int)mg::launch_pdl(matvec_q6k_limbs_long_kernel<FROM_X>, dim3((unsigned)grid), dim3(kQ6LongThreads), smem,
+                                   (cudaStream_t)stream, w, src, add, y, out_dim, bpr, x_aligned);
+    }
+    constexpr int R = 2;
+    static size_t configured = 0;
+    if (int rc = q6_allow_smem(matvec_q6k_limbs_kernel<R, FROM_X>, smem, configured)) return rc;
+    // CTAs an SM holds: by shared memory (1 KiB reserved per CTA) and by threads
+    int per_sm = (int)((228u * 1024u) / (smem + 1024));
+    per_sm = per_sm > 2048 / kQ6LimbThreads ? 2048 / kQ6LimbThreads : (per_sm < 1 ? 1 : per_sm);
+    int grid = (out_dim + R * kQ6LimbWarps - 1) / (R * kQ6LimbWarps);
+    if (grid > dp.sm_count * per_sm) grid = dp.sm_count * per_sm;
+    return (int)mg::launch_pdl(matvec_q6k_limbs_kernel<R, FROM_X>, dim3((unsigned)grid), dim3(kQ6LimbThreads), smem,
+                               (cudaStream_t)stream, w, src, add, y, out_dim, bpr, x_aligned);
+}
+
+// x_kind 0: f32 activations; 1: limb records (Q6_K only).
+template <int KIND>
+int matvec_any(const uint8_t* w, const void* src, int x_kind, const float* add, float* y, int out_dim, int bpr, void* stream) {
+    if (out_dim <= 0 || bpr <= 0 || !w || !src || !y || (x_kind != 0 && x_kind != 1)) return (int)cudaErrorInvalidValue;
+    if (KIND == 5 && (!mg::aligned16(w) || x_kind != 0)) return (int)cudaErrorInvalidValue;
     if (KIND == 6 && (reinterpret_cast<uintptr_t>(w) & 1u)) return (int)cudaErrorInvalidValue;
-    return (int)mg::launch_pdl(matvec_kquant_kernel<KIND>, dim3((unsigned)grid_for(out_dim)), dim3(kThreads), 0,
-                               (cudaStream_t)stream, w, x, y, out_dim, bpr);
+    if (KIND == 6 && x_kind == 1) {
+        if (!q6_limbs_ok(w, bpr) || !mg::aligned16(src)) return (int)cudaErrorInvalidValue;
+        return launch_q6_limbs<0>(w, src, add, y, out_dim, bpr, stream);
+    }
+    if (KIND == 6 && q6_limbs_ok(w, bpr)) return launch_q6_limbs<1>(w, src, add, y, out_dim, bpr, stream);
+    return launch_matvec<KIND>(w, static_cast<const float*>(src), add, y, out_dim, bpr, stream);
 }
 
 }  // namespace
@@ -197,17 +594,27 @@ extern "C" {
 
 int launch_matvec_q5k_on_stream(const uint8_t* w_q5, const float* x, float* y, int out_dim, int blocks_per_row,
                                 void* stream) {
-    return launch_matvec<5>(w_q5, x, y, out_dim, blocks_per_row, stream);
+    return matvec_any<5>(w_q5, x, 0, nullptr, y, out_dim, blocks_per_row, stream);
 }
 int launch_matvec_q5k(const uint8_t* w_q5, const float* x, float* y, int out_dim, int blocks_per_row) {
-    return launch_matvec<5>(w_q5, x, y, out_dim, blocks_per_row, nullptr);
+    return matvec_any<5>(w_q5, x, 0, nullptr, y, out_dim, blocks_per_row, nullptr);
 }
 int launch_matvec_q6k_on_stream(const uint8_t* w_q6, const float* x, float* y, int out_dim, int blocks_per_row,
                                 void* stream) {
-    return launch_matvec<6>(w_q6, x, y, out_dim, blocks_per_row, stream);
+    return matvec_any<6>(w_q6, x, 0, nullptr, y, out_dim, blocks_per_row, stream);
 }
 int launch_matvec_q6k(const uint8_t* w_q6, const float* x, float* y, int out_dim, int blocks_per_row) {
-    return launch_matvec<6>(w_q6, x, y, out_dim, blocks_per_row, nullptr);
+    return matvec_any<6>(w_q6, x, 0, nullptr, y, out_dim, blocks_per_row, nullptr);
+}
+// y[row] = (add ? add[row] : 0) + W[row] . x for a Q5_K (ggml_type 13) or Q6_K (14) weight: the matvec
+// with the residual add the decode loop puts behind it (crates/modgrad-gemma/src/rocm_gemma.rs:470-475,
+// :497-500) folded in; y may alias add.  x_kind 0: x is the f32 activation vector; 1 (Q6_K only, weight
+// 4-byte aligned): x holds the limb records of mg_q4k_x_to_limbs_on_stream / mg_swiglu_limbs_on_stream.
+int mg_matvec_kquant_on_stream(int ggml_type, const uint8_t* w, const void* x, int x_kind, const float* add, float* y,
+                               int out_dim, int blocks_per_row, void* stream) {
+    if (ggml_type == 13) return matvec_any<5>(w, x, x_kind, add, y, out_dim, blocks_per_row, stream);
+    if (ggml_type == 14) return matvec_any<6>(w, x, x_kind, add, y, out_dim, blocks_per_row, stream);
+    return (int)cudaErrorInvalidValue;
 }
 
 int launch_matvec_q6k_dp4a_on_stream(const uint8_t* w, const int8_t* xq, const float* xd, const float* xsum, float* y,
@@ -221,6 +628,28 @@ int launch_matvec_q6k_dp4a_on_stream(const uint8_t* w, const int8_t* xq, const f
 int launch_matvec_q6k_dp4a(const uint8_t* w, const int8_t* xq, const float* xd, const float* xsum, float* y, int out_dim,
                            int bpr) {
     return launch_matvec_q6k_dp4a_on_stream(w, xq, xd, xsum, y, out_dim, bpr, nullptr);
+}
+
+// ggml_type: 12 (Q4_K), 13 (Q5_K) or 14 (Q6_K); d_model a multiple of 256.
+int mg_embed_kquant_on_stream(const void* table, int ggml_type, int token, const int* token_dev, float* out, int d_model,
+                              int vocab, void* stream) {
+    if (!table || !out || d_model <= 0 || d_model % 256 || vocab <= 0) return (int)cudaErrorInvalidValue;
+    const int bpr = d_model / 256;
+    const uint8_t* t = static_cast<const uint8_t*>(table);
+    const dim3 grid((unsigned)((bpr + kWarps - 1) / kWarps)), block(kThreads);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (ggml_type) {
+        case 12:
+            if (!mg::aligned16(t)) return (int)cudaErrorInvalidValue;
+            return (int)mg::launch_pdl(embed_kquant_kernel<4>, grid, block, 0, st, t, token_dev, token, out, bpr, vocab);
+        case 13:
+            if (!mg::aligned16(t)) return (int)cudaErrorInvalidValue;
+            return (int)mg::launch_pdl(embed_kquant_kernel<5>, grid, block, 0, st, t, token_dev, token, out, bpr, vocab);
+        case 14:
+            if (reinterpret_cast<uintptr_t>(t) & 1u) return (int)cudaErrorInvalidValue;
+            return (int)mg::launch_pdl(embed_kquant_kernel<6>, grid, block, 0, st, t, token_dev, token, out, bpr, vocab);
+        default: return (int)cudaErrorInvalidValue;
+    }
 }
 
 int mg_dequant_q5k_on_stream(const uint8_t* q5k, int n_blocks, float* fp32_out, void* stream) {

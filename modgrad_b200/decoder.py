@@ -106,14 +106,25 @@ def _p(a: np.ndarray):
 class Q4KDecoder:
     """Device-resident decoder; one graph launch per token."""
 
-    def __init__(self, cfg: DecoderConfig, rank: int = 0, world: int = 1, nccl_id: bytes | None = None):
+    def __init__(self, cfg: DecoderConfig, rank: int = 0, world: int = 1, nccl_id: bytes | None = None,
+                 types: tuple | None = None):
+        """``types`` = (proj_types, embed_type, head_type) builds the typed single-GPU engine: proj_types
+        holds, per layer, the GGUF type ids (12 Q4_K, 13 Q5_K, 14 Q6_K) of q, k, v, o, gate, up, down;
+        embed_type / head_type are 1 (F16) or one of the three."""
         self.cfg = cfg
         self.shard = shard_mod.decoder_shard(cfg, rank, world)
         self._lib = _lib.load()
         h = C.c_void_p()
         cs = cfg.c_struct()
         idbuf = C.create_string_buffer(nccl_id, 128) if nccl_id is not None else None
-        code = self._lib.mg_decoder_create_sharded(C.byref(cs), rank, world, idbuf, C.byref(h))
+        if types is not None:
+            if world != 1:
+                raise Runtime("the typed engine runs on one GPU")
+            proj, embed_type, head_type = types
+            flat = np.ascontiguousarray(np.asarray(proj, dtype=np.int32).reshape(cfg.n_layers * 7))
+            code = self._lib.mg_decoder_create_typed(C.byref(cs), _p(flat), int(embed_type), int(head_type), C.byref(h))
+        else:
+            code = self._lib.mg_decoder_create_sharded(C.byref(cs), rank, world, idbuf, C.byref(h))
         if code != 0 or not h.value:
             raise Runtime(f"mg_decoder_create: {self._lib.mg_get_error_string(code).decode()}")
         self._h = h.value
@@ -149,6 +160,10 @@ class Q4KDecoder:
         """(base device pointer, bytes) of the single allocation that holds every weight tensor."""
         n = C.c_size_t()
         return int(self._lib.mg_decoder_weight_arena(self._h, C.byref(n)) or 0), n.value
+
+    def weight_type(self, layer: int, which: int) -> int:
+        """GGUF type id of one weight tensor (0 for the f32 norms)."""
+        return int(self._lib.mg_decoder_weight_type(self._h, layer, which))
 
     def weight_ptr(self, layer: int, which: int) -> int:
         return int(self._lib.mg_decoder_weight_ptr(self._h, layer, which) or 0)

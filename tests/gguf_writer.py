@@ -10,7 +10,7 @@ import numpy as np
 T_U8, T_I8, T_U16, T_I16, T_U32, T_I32, T_F32, T_BOOL, T_STR, T_ARR, T_U64, T_I64, T_F64 = range(13)
 _FMT = {T_U8: "<B", T_I8: "<b", T_U16: "<H", T_I16: "<h", T_U32: "<I", T_I32: "<i", T_F32: "<f", T_BOOL: "<B",
         T_U64: "<Q", T_I64: "<q", T_F64: "<d"}
-GGML_F32, GGML_F16, GGML_Q4_K = 0, 1, 12
+GGML_F32, GGML_F16, GGML_Q4_K, GGML_Q5_K, GGML_Q6_K = 0, 1, 12, 13, 14
 
 
 def _string(s: str) -> bytes:
@@ -48,7 +48,9 @@ def write_gguf(meta: list, tensors: list, version: int = 3, align: int = 32) -> 
 
 def decoder_gguf(cfg, layers: list, g: dict, arch: str = "qwen2", tied: bool = False) -> bytes:
     """A checkpoint of the decoder architecture the engine runs, from host tensors:
-    layers[l] = dict(wq, wk, wv, wo, wgate, wup, wdown, attn_norm, ffn_norm), g = dict(embed, lm_head, out_norm)."""
+    layers[l] = dict(wq, wk, wv, wo, wgate, wup, wdown, attn_norm, ffn_norm), g = dict(embed, lm_head, out_norm).
+    A layer's optional "types" maps a projection key to its GGML type (default Q4_K); g's optional
+    "embed_type" / "head_type" give the types of the embedding and the LM head (default F16)."""
     meta = [("general.architecture", T_STR, arch), (f"{arch}.block_count", T_U32, cfg.n_layers),
             (f"{arch}.embedding_length", T_U32, cfg.d_model), (f"{arch}.feed_forward_length", T_U32, cfg.d_ff),
             (f"{arch}.attention.head_count", T_U32, cfg.n_heads), (f"{arch}.attention.head_count_kv", T_U32, cfg.n_kv_heads),
@@ -56,16 +58,16 @@ def decoder_gguf(cfg, layers: list, g: dict, arch: str = "qwen2", tied: bool = F
             (f"{arch}.attention.layer_norm_rms_epsilon", T_F32, cfg.rms_eps), (f"{arch}.rope.freq_base", T_F32, cfg.rope_base),
             ("tokenizer.ggml.tokens", T_ARR, (T_STR, ["<a>", "<b>", "c"])), ("general.alignment", T_U32, 32)]
     D, F = cfg.d_model, cfg.d_ff
-    ts = [("token_embd.weight", (D, cfg.vocab), GGML_F16, g["embed"])]
+    ts = [("token_embd.weight", (D, cfg.vocab), g.get("embed_type", GGML_F16), g["embed"])]
     names = {"wq": ("attn_q", D, cfg.q_dim), "wk": ("attn_k", D, cfg.kv_dim), "wv": ("attn_v", D, cfg.kv_dim),
              "wo": ("attn_output", cfg.q_dim, D), "wgate": ("ffn_gate", D, F), "wup": ("ffn_up", D, F),
              "wdown": ("ffn_down", F, D)}
     for l, lw in enumerate(layers):
         for k, (n, i, o) in names.items():
-            ts.append((f"blk.{l}.{n}.weight", (i, o), GGML_Q4_K, lw[k]))
+            ts.append((f"blk.{l}.{n}.weight", (i, o), lw.get("types", {}).get(k, GGML_Q4_K), lw[k]))
         ts.append((f"blk.{l}.attn_norm.weight", (D,), GGML_F32, lw["attn_norm"]))
         ts.append((f"blk.{l}.ffn_norm.weight", (D,), GGML_F32, lw["ffn_norm"]))
     ts.append(("output_norm.weight", (D,), GGML_F32, g["out_norm"]))
     if not tied:
-        ts.append(("output.weight", (D, cfg.vocab), GGML_F16, g["lm_head"]))
+        ts.append(("output.weight", (D, cfg.vocab), g.get("head_type", GGML_F16), g["lm_head"]))
     return write_gguf(meta, ts)

@@ -66,13 +66,71 @@ def test_kquant_dequant_random_blocks_bit_exact(orc, cuda, kind, n_blocks):
 
 
 @pytest.mark.parametrize("kind", [5, 6])
-@pytest.mark.parametrize("out_dim,bpr", [(1, 1), (7, 3), (513, 14), (3584, 74), (4096, 16), (9000, 14)])
+@pytest.mark.parametrize("out_dim,bpr", [(1, 1), (7, 3), (513, 14), (3584, 74), (4096, 16), (9000, 14), (100, 40),
+                                         (5000, 33), (149, 264)])
 def test_kquant_matvec(orc, cuda, kind, out_dim, bpr):
     rng = np.random.Generator(np.random.PCG64(400 + out_dim + bpr + kind))
     w = synth.kquant_matrix(kind, out_dim, bpr * 256, rng)
     x = synth.activations(bpr * 256, rng)
     y = gpu_matvec(cuda, kind, w, x, out_dim, bpr)
     assert rel_rms_err(y, orc.matvec_kquant_f64(kind, w, x, out_dim, bpr)) <= GEMV_TOL
+
+
+@pytest.mark.parametrize("kind,out_dim,bpr,x_kind", [(6, 3584, 74, 1), (6, 3585, 14, 1), (6, 33, 3, 1), (6, 3584, 74, 0),
+                                                     (6, 640, 14, 0), (5, 3584, 74, 0), (5, 129, 14, 0)])
+def test_kquant_matvec_with_residual_and_limb_records(orc, cuda, kind, out_dim, bpr, x_kind):
+    """mg_matvec_kquant_on_stream: y = add + W x in place, from f32 activations or (Q6_K) from limb records."""
+    rng = np.random.Generator(np.random.PCG64(900 + out_dim + bpr + kind + x_kind))
+    k = bpr * 256
+    w = synth.kquant_matrix(kind, out_dim, k, rng)
+    x = synth.activations(k, rng)
+    add = synth.activations(out_dim, rng) * np.float32(3.0)
+    wd, xd, yd = upload(w), upload(x), upload(add)
+    src = xd
+    if x_kind == 1:
+        src = DeviceBuffer(cuda.mg_q4k_limb_record_bytes(k))
+        assert cuda.mg_q4k_x_to_limbs_on_stream(xd.ptr, k, src.ptr, None) == 0
+    assert cuda.mg_matvec_kquant_on_stream(8 + kind, wd.ptr, src.ptr, x_kind, yd.ptr, yd.ptr, out_dim, bpr, None) == 0
+    kern.sync()
+    want = orc.matvec_kquant_f64(kind, w, x, out_dim, bpr)
+    got = yd.copy_to_host(out_dim).astype(np.float64) - add.astype(np.float64)
+    assert rms(got - want) / rms(want) <= GEMV_TOL
+    # without the addend
+    y2 = DeviceBuffer(out_dim * 4)
+    assert cuda.mg_matvec_kquant_on_stream(8 + kind, wd.ptr, src.ptr, x_kind, None, y2.ptr, out_dim, bpr, None) == 0
+    kern.sync()
+    assert rel_rms_err(y2.copy_to_host(out_dim), want) <= GEMV_TOL
+
+
+def test_q6k_weight_that_is_only_two_byte_aligned(orc, cuda):
+    """Q6_K rows are 2-byte aligned; a weight that starts 2 bytes into a word takes the float kernel and refuses records."""
+    out_dim, bpr = 300, 14
+    rng = np.random.Generator(np.random.PCG64(93))
+    w = synth.kquant_matrix(6, out_dim, bpr * 256, rng)
+    x = synth.activations(bpr * 256, rng)
+    buf = DeviceBuffer(w.nbytes + 16)
+    shifted = np.concatenate([np.zeros(2, dtype=np.uint8), w, np.zeros(14, dtype=np.uint8)])
+    buf.copy_from_host_bytes(shifted)
+    xd, yd = upload(x), DeviceBuffer(out_dim * 4)
+    assert cuda.launch_matvec_q6k(buf.ptr + 2, xd.ptr, yd.ptr, out_dim, bpr) == 0
+    kern.sync()
+    assert rel_rms_err(yd.copy_to_host(out_dim), orc.matvec_kquant_f64(6, w, x, out_dim, bpr)) <= GEMV_TOL
+    rec = DeviceBuffer(cuda.mg_q4k_limb_record_bytes(bpr * 256))
+    assert cuda.mg_q4k_x_to_limbs_on_stream(xd.ptr, bpr * 256, rec.ptr, None) == 0
+    assert cuda.mg_matvec_kquant_on_stream(14, buf.ptr + 2, rec.ptr, 1, None, yd.ptr, out_dim, bpr, None) == 1
+    assert cuda.mg_matvec_kquant_on_stream(13, buf.ptr, rec.ptr, 1, None, yd.ptr, out_dim, bpr, None) == 1   # Q5_K: f32 only
+    assert cuda.mg_matvec_kquant_on_stream(12, buf.ptr, xd.ptr, 0, None, yd.ptr, out_dim, bpr, None) == 1
+    kern.sync()
+
+
+def test_q6k_non_finite_activation_poisons_every_row(cuda):
+    out_dim, bpr = 64, 14
+    rng = np.random.Generator(np.random.PCG64(94))
+    w = synth.kquant_matrix(6, out_dim, bpr * 256, rng)
+    x = synth.activations(bpr * 256, rng)
+    x[1000] = np.inf
+    y = gpu_matvec(cuda, 6, w, x, out_dim, bpr)
+    assert np.all(np.isnan(y))
 
 
 def test_kquant_matvec_equals_dequant_then_dot(cuda):
