@@ -303,26 +303,28 @@ __device__ __forceinline__ uint32_t q6_signed4(uint32_t lo, uint32_t h) {
     return (q ^ 0x20202020u) + neg * 6u;                  // bit 5 flipped, bits 6 and 7 set where negative
 }
 
-// R rows' dot products with one block of activations: acc[r] += d_r * sum_k sc_rk * s_k * <q_rk, a_k> for the
-// 32 weights of lane (G, qtr).  wr[r]: row r; rec_w: the records of the whole vector.
+// The 32 weights of lane (G, qtr) in one block, still packed, with their four scale bytes and d.
+struct Q6Lane {
+    uint2 ql0, ql1, qh;
+    int sc[4];
+    uint32_t d_bits;
+};
+__device__ __forceinline__ void q6_load(Q6Lane& t, const uint8_t* b, int G, int qtr) {
+    t.ql0 = ld8_align2(b + 64 * G + 8 * qtr);
+    t.ql1 = ld8_align2(b + 64 * G + 32 + 8 * qtr);
+    t.qh = ld8_align2(b + 128 + 32 * G + 8 * qtr);
+    const int8_t* s8 = reinterpret_cast<const int8_t*>(b + 192 + 8 * G + (qtr >> 1));
+#pragma unroll
+    for (int k = 0; k < 4; ++k) t.sc[k] = (int)s8[2 * k];
+    t.d_bits = *reinterpret_cast<const uint16_t*>(b + 208);
+}
+// R rows' dot products with block `blk` of the activations: acc[r] += d_r * sum_k sc_rk * s_k * <q_rk, a_k>.
+// rec_w: the limb records of the whole vector.
 template <int R>
-__device__ __forceinline__ void q6_block_dot(const uint8_t* const (&wr)[R], const uint32_t* rec_w, int blk, int G, int qtr,
-                                             float (&acc)[R]) {
-    uint2 ql0[R], ql1[R], qh[R];
-    int sc[R][4];
-    float d[R], part[R];
+__device__ __forceinline__ void q6_dot(const Q6Lane (&t)[R], const uint32_t* rec_w, int blk, int G, int qtr, float (&acc)[R]) {
+    float part[R];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const uint8_t* b = wr[r] + (size_t)blk * kQ6Bytes;
-        ql0[r] = ld8_align2(b + 64 * G + 8 * qtr);
-        ql1[r] = ld8_align2(b + 64 * G + 32 + 8 * qtr);
-        qh[r] = ld8_align2(b + 128 + 32 * G + 8 * qtr);
-        const int8_t* s8 = reinterpret_cast<const int8_t*>(b + 192 + 8 * G + (qtr >> 1));
-#pragma unroll
-        for (int k = 0; k < 4; ++k) sc[r][k] = (int)s8[2 * k];
-        d[r] = q4k::half_bits_finite_or_zero(*reinterpret_cast<const uint16_t*>(b + 208));
-        part[r] = 0.0f;
-    }
+    for (int r = 0; r < R; ++r) part[r] = 0.0f;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         // activations of sub-block 4G + k: record 2G + k/2, low or high plane set, words 2qtr, 2qtr + 1
@@ -334,22 +336,22 @@ __device__ __forceinline__ void q6_block_dot(const uint8_t* const (&wr)[R], cons
         const float s = __uint_as_float(rp[48 + (k & 1)]);
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-            const uint2 lo = (k & 1) ? ql1[r] : ql0[r];
+            const uint2 lo = (k & 1) ? t[r].ql1 : t[r].ql0;
             uint32_t qa, qb;
-            if (k == 0) { qa = q6_signed4<0>(lo.x, qh[r].x); qb = q6_signed4<0>(lo.y, qh[r].y); }
-            else if (k == 1) { qa = q6_signed4<1>(lo.x, qh[r].x); qb = q6_signed4<1>(lo.y, qh[r].y); }
-            else if (k == 2) { qa = q6_signed4<2>(lo.x, qh[r].x); qb = q6_signed4<2>(lo.y, qh[r].y); }
-            else { qa = q6_signed4<3>(lo.x, qh[r].x); qb = q6_signed4<3>(lo.y, qh[r].y); }
+            if (k == 0) { qa = q6_signed4<0>(lo.x, t[r].qh.x); qb = q6_signed4<0>(lo.y, t[r].qh.y); }
+            else if (k == 1) { qa = q6_signed4<1>(lo.x, t[r].qh.x); qb = q6_signed4<1>(lo.y, t[r].qh.y); }
+            else if (k == 2) { qa = q6_signed4<2>(lo.x, t[r].qh.x); qb = q6_signed4<2>(lo.y, t[r].qh.y); }
+            else { qa = q6_signed4<3>(lo.x, t[r].qh.x); qb = q6_signed4<3>(lo.y, t[r].qh.y); }
             const int i2 = gemvdev::dp4a_ss(qb, a2.y, gemvdev::dp4a_ss(qa, a2.x, 0));
             const int i1 = dp4a_su(qb, a1.y, dp4a_su(qa, a1.x, 0));
             const int i0 = dp4a_su(qb, a0.y, dp4a_su(qa, a0.x, 0));
             // |i2| <= 2^15, |i1 * 256 + i0| < 2^24: both conversions are exact
             const float f = fmaf((float)i2, 65536.0f, (float)(i1 * 256 + i0));
-            part[r] = fmaf(f * s, (float)sc[r][k], part[r]);
+            part[r] = fmaf(f * s, (float)t[r].sc[k], part[r]);
         }
     }
 #pragma unroll
-    for (int r = 0; r < R; ++r) acc[r] = fmaf(d[r], part[r], acc[r]);
+    for (int r = 0; r < R; ++r) acc[r] = fmaf(q4k::half_bits_finite_or_zero(t[r].d_bits), part[r], acc[r]);
 }
 
 // The activation vector as limb records in shared memory.  FROM_X = 1: src is the f32 vector, converted
@@ -378,7 +380,7 @@ constexpr int kQ6LimbThreads = 256, kQ6LimbWarps = kQ6LimbThreads / 32;
 // Short rows, many of them: a warp owns R rows at a time and walks their blocks four per step.
 // y[row] = (add ? add[row] : 0) + W[row] . x.
 template <int R, int FROM_X>
-__global__ void __launch_bounds__(kQ6LimbThreads) matvec_q6k_limbs_kernel(const uint8_t* __restrict__ w, const void* src,
+__global__ void __launch_bounds__(kQ6LimbThreads, 4) matvec_q6k_limbs_kernel(const uint8_t* __restrict__ w, const void* src,
                                                                           const float* add, float* y, int out_dim, int bpr,
                                                                           int x_aligned) {
     extern __shared__ __align__(16) uint4 rec_s[];
@@ -397,7 +399,12 @@ __global__ void __launch_bounds__(kQ6LimbThreads) matvec_q6k_limbs_kernel(const 
             acc[r] = 0.0f;
             wr[r] = w + (size_t)min(row0 + r, out_dim - 1) * row_bytes;   // a row past the end repeats the last one
         }
-        for (int blk = bsel; blk < bpr; blk += 4) q6_block_dot<R>(wr, rec_w, blk, G, qtr, acc);
+        for (int blk = bsel; blk < bpr; blk += 4) {
+            Q6Lane t[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) q6_load(t[r], wr[r] + (size_t)blk * kQ6Bytes, G, qtr);
+            q6_dot<R>(t, rec_w, blk, G, qtr, acc);
+        }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const float t = q4k::warp_sum(acc[r]);
@@ -419,15 +426,21 @@ __global__ void __launch_bounds__(kQ6LongThreads, 1) matvec_q6k_limbs_long_kerne
     extern __shared__ __align__(16) uint4 rec_s[];
     const uint32_t* rec_w = reinterpret_cast<const uint32_t*>(rec_s);
     float* part = reinterpret_cast<float*>(rec_s + (size_t)bpr * 4 * xlimbs::kRecordVec4);   // [kQ6LongRows][kQ6LongGroups]
-    mg::pdl_prologue();
-    q6_stage_records<FROM_X, kQ6LongThreads>(src, bpr, x_aligned, rec_s);
-
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int group = threadIdx.x >> 3, G = (lane >> 2) & 1, qtr = lane & 3;
     const unsigned gmask = 0xFFu << (lane & 24);   // the eight lanes of this group
     const size_t row_bytes = (size_t)bpr * kQ6Bytes;
     const int row_begin = (int)((long long)blockIdx.x * out_dim / gridDim.x);
     const int row_end = (int)((long long)(blockIdx.x + 1) * out_dim / gridDim.x);
+    const int step_rows = kQ6LongGroups / bpr, step_blks = kQ6LongGroups - step_rows * bpr;   // one stride of a group
+    // The weights do not depend on the kernel before this one: the first block is requested before the
+    // wait for the activations, the next one always before the current one is multiplied.
+    Q6Lane nxt[1];
+    if (group < min(kQ6LongRows, row_end - row_begin) * bpr)
+        q6_load(nxt[0], w + (size_t)row_begin * row_bytes + (size_t)group * kQ6Bytes, G, qtr);
+    mg::pdl_prologue();
+    q6_stage_records<FROM_X, kQ6LongThreads>(src, bpr, x_aligned, rec_s);
+
     for (int pass0 = row_begin; pass0 < row_end; pass0 += kQ6LongRows) {
         const int n_rows = min(kQ6LongRows, row_end - pass0);
         for (int i = threadIdx.x; i < kQ6LongRows * kQ6LongGroups; i += kQ6LongThreads) part[i] = 0.0f;
@@ -435,8 +448,10 @@ __global__ void __launch_bounds__(kQ6LongThreads, 1) matvec_q6k_limbs_long_kerne
         const int n_items = n_rows * bpr;
         int cur = -1;
         float acc[1] = {0.0f};
+        const uint8_t* wp = w + (size_t)pass0 * row_bytes;   // rows of a pass are one contiguous run of blocks
+        if (pass0 != row_begin && group < n_items) q6_load(nxt[0], wp + (size_t)group * kQ6Bytes, G, qtr);
+        int rl = group / bpr, blk = group - rl * bpr;   // (row, block) of item j
         for (int j = group; j < n_items; j += kQ6LongGroups) {
-            const int rl = j / bpr, blk = j - rl * bpr;
             if (rl != cur) {   // the whole group moves on together
                 if (cur >= 0) {
                     float v = acc[0];
@@ -448,8 +463,13 @@ __global__ void __launch_bounds__(kQ6LongThreads, 1) matvec_q6k_limbs_long_kerne
                 cur = rl;
                 acc[0] = 0.0f;
             }
-            const uint8_t* wr[1] = {w + (size_t)(pass0 + rl) * row_bytes};
-            q6_block_dot<1>(wr, rec_w, blk, G, qtr, acc);
+            Q6Lane now[1];
+            now[0] = nxt[0];
+            if (j + kQ6LongGroups < n_items) q6_load(nxt[0], wp + (size_t)(j + kQ6LongGroups) * kQ6Bytes, G, qtr);
+            q6_dot<1>(now, rec_w, blk, G, qtr, acc);
+            rl += step_rows;
+            blk += step_blks;
+            if (blk >= bpr) { blk -= bpr; ++rl; }
         }
         if (cur >= 0) {
             float v = acc[0];
@@ -459,11 +479,11 @@ __global__ void __launch_bounds__(kQ6LongThreads, 1) matvec_q6k_limbs_long_kerne
             if ((lane & 7) == 0) part[cur * kQ6LongGroups + group] = v;
         }
         __syncthreads();
-        for (int rl = warp; rl < n_rows; rl += kQ6LongThreads / 32) {
-            const float* pr = part + rl * kQ6LongGroups;
+        for (int rr = warp; rr < n_rows; rr += kQ6LongThreads / 32) {
+            const float* pr = part + rr * kQ6LongGroups;
             float t = (pr[lane] + pr[32 + lane]) + pr[64 + lane];
             t = q4k::warp_sum(t);
-            if (lane == 0) y[pass0 + rl] = add ? add[pass0 + rl] + t : t;
+            if (lane == 0) y[pass0 + rr] = add ? add[pass0 + rr] + t : t;
         }
         __syncthreads();   // before the partial sums are cleared for the next rows
     }
@@ -526,18 +546,22 @@ int launch_matvec(const uint8_t* w, const float* x, const float* add, float* y, 
     return launch_matvec_shape<KIND, 4, 4>(w, x, add, y, out_dim, bpr, stream);
 }
 
-// Rows longer than this take the kernel that splits a row's blocks over a whole CTA.
-constexpr int kQ6LongMinBpr = 33;
+// Few rows per SM (one pass of the long kernel), or rows of more than 32 blocks: the kernel that splits
+// the rows' blocks over a whole CTA.  Many short rows: a warp per pair of rows.
+bool q6_long_shape(int out_dim, int bpr) {
+    const mg::DeviceProps& dp = mg::device_props();
+    return bpr > 32 || out_dim <= (dp.ok ? dp.sm_count : 148) * kQ6LongRows;
+}
 
 // The limb kernels need the weight 4-byte aligned (their 8-byte loads round the address down) and the
 // whole activation vector as records in one CTA's shared memory.
-size_t q6_smem_bytes(int bpr) {
+size_t q6_smem_bytes(int out_dim, int bpr) {
     return (size_t)bpr * 4 * xlimbs::kRecordBytes +
-           (bpr >= kQ6LongMinBpr ? (size_t)kQ6LongRows * kQ6LongGroups * sizeof(float) : 0);
+           (q6_long_shape(out_dim, bpr) ? (size_t)kQ6LongRows * kQ6LongGroups * sizeof(float) : 0);
 }
-bool q6_limbs_ok(const uint8_t* w, int bpr) {
+bool q6_limbs_ok(const uint8_t* w, int out_dim, int bpr) {
     const mg::DeviceProps& dp = mg::device_props();
-    return (reinterpret_cast<uintptr_t>(w) & 3u) == 0 && dp.ok && q6_smem_bytes(bpr) <= (size_t)dp.max_smem_optin;
+    return (reinterpret_cast<uintptr_t>(w) & 3u) == 0 && dp.ok && q6_smem_bytes(out_dim, bpr) <= (size_t)dp.max_smem_optin;
 }
 
 template <class Kernel>
@@ -553,9 +577,9 @@ int q6_allow_smem(Kernel kernel, size_t smem, size_t& configured) {
 template <int FROM_X>
 int launch_q6_limbs(const uint8_t* w, const void* src, const float* add, float* y, int out_dim, int bpr, void* stream) {
     const mg::DeviceProps& dp = mg::device_props();
-    const size_t smem = q6_smem_bytes(bpr);
+    const size_t smem = q6_smem_bytes(out_dim, bpr);
     const int x_aligned = mg::aligned16(src) ? 1 : 0;
-    if (bpr >= kQ6LongMinBpr) {
+    if (q6_long_shape(out_dim, bpr)) {
         static size_t configured = 0;   // the largest dynamic shared memory the kernel was configured for
         if (int rc = q6_allow_smem(matvec_q6k_limbs_long_kernel<FROM_X>, smem, configured)) return rc;
         const int grid = out_dim < dp.sm_count ? out_dim : dp.sm_count;
@@ -581,10 +605,10 @@ int matvec_any(const uint8_t* w, const void* src, int x_kind, const float* add, 
     if (KIND == 5 && (!mg::aligned16(w) || x_kind != 0)) return (int)cudaErrorInvalidValue;
     if (KIND == 6 && (reinterpret_cast<uintptr_t>(w) & 1u)) return (int)cudaErrorInvalidValue;
     if (KIND == 6 && x_kind == 1) {
-        if (!q6_limbs_ok(w, bpr) || !mg::aligned16(src)) return (int)cudaErrorInvalidValue;
+        if (!q6_limbs_ok(w, out_dim, bpr) || !mg::aligned16(src)) return (int)cudaErrorInvalidValue;
         return launch_q6_limbs<0>(w, src, add, y, out_dim, bpr, stream);
     }
-    if (KIND == 6 && q6_limbs_ok(w, bpr)) return launch_q6_limbs<1>(w, src, add, y, out_dim, bpr, stream);
+    if (KIND == 6 && q6_limbs_ok(w, out_dim, bpr)) return launch_q6_limbs<1>(w, src, add, y, out_dim, bpr, stream);
     return launch_matvec<KIND>(w, static_cast<const float*>(src), add, y, out_dim, bpr, stream);
 }
 
