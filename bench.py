@@ -205,6 +205,9 @@ def main():
     ap.add_argument("--matmul-only", action="store_true", help="run only the tensor-core leg (profiling)")
     ap.add_argument("--matmul-reps", type=int, default=20)
     ap.add_argument("--no-layer70b", action="store_true", help="skip the 70B-class sharded layer leg")
+    ap.add_argument("--no-kquant", action="store_true", help="skip the Q5_K / Q6_K matvec and mixed-checkpoint decode leg")
+    ap.add_argument("--kquant-only", action="store_true", help="run only the K-quant leg (profiling)")
+    ap.add_argument("--kquant-no-decode", action="store_true", help="K-quant leg without the mixed-checkpoint decode")
     ap.add_argument("--decode-tokens", type=int, default=256)
     ap.add_argument("--decode-prefill", type=int, default=2048)
     args = ap.parse_args()
@@ -232,6 +235,9 @@ def main():
         return
     if args.matmul_only:
         print(json.dumps({"matmul_tc": matmul_leg(args, torch, lib, dev)}), flush=True)
+        return
+    if args.kquant_only:
+        print(json.dumps({"kquant": kquant_leg(args, torch, lib, dev)}), flush=True)
         return
 
     # ---- inputs: generated on the host, uploaded verbatim, resident before timing ----------
@@ -454,6 +460,9 @@ def main():
         if world == 1 and not args.no_decode:
             torch.cuda.empty_cache()
             line["decode"] = decode_leg(args)
+        if world == 1 and not args.no_kquant:
+            torch.cuda.empty_cache()
+            line["kquant"] = kquant_leg(args, torch, lib, dev)
         if world > 1 and decode_sharded is not None:
             line["decode"] = decode_sharded
         if layer70b is not None:
@@ -799,6 +808,97 @@ def decode_leg(args):
            "hbm_frac": round(bpt / ms_tok / 1e6 / peak, 4), "peak_source": f"of {kind}",
            "kernels_per_token": d.kernels_per_token(), "load_s": round(load_s, 1),
            "model": "qwen2.5-7b-shaped, random-init, Q4_K linears"}
+    d.close()
+    return out
+
+
+def kquant_leg(args, torch, lib, dev):
+    """The other K-quants of a real checkpoint.  (1) Q5_K / Q6_K batch-1 matvecs on the 7B shapes where such
+    tensors occur (attn_v, ffn_down, the LM head), weights rotated through > 400 MB of copies, CUDA events
+    around back-to-back launches; Q6_K also from limb records with the residual add folded in, as the typed
+    engine calls it.  (2) Greedy decode of the 7B-class model with the tensor types of a Q4_K_M-style file:
+    attn_v and ffn_down Q6_K in half of the layers, Q4_K token embedding, Q6_K LM head, the rest Q4_K."""
+    from modgrad_b200 import decoder as dec
+    rng = np.random.Generator(np.random.PCG64(77))
+    stream = torch.cuda.current_stream().cuda_stream
+    peak, kind = measured_peak()
+    block_bytes = {5: 176, 6: 210}
+    shapes = []
+    for knd, name in ((5, "q5k"), (6, "q6k")):
+        for label, rows, cols in (("attn_v", 512, 3584), ("ffn_down", 3584, 18944), ("lm_head", 152064, 3584)):
+            one = synth.kquant_matrix(knd, rows, cols, rng)
+            copies = max(2, int(400e6 // one.size) + 1)
+            w = torch.empty(copies * one.size, dtype=torch.uint8, device=dev)
+            w.view(copies, one.size)[:] = torch.from_numpy(one).to(dev)
+            x = torch.randn(cols, device=dev)
+            y = torch.zeros(rows, device=dev)
+            rec = torch.empty(lib.mg_q4k_limb_record_bytes(cols), dtype=torch.uint8, device=dev)
+            assert lib.mg_q4k_x_to_limbs_on_stream(x.data_ptr(), cols, rec.data_ptr(), stream) == 0
+            variants = [("f32 x", lambda c: lib.mg_matvec_kquant_on_stream(8 + knd, w.data_ptr() + c * one.size, x.data_ptr(), 0,
+                                                                           None, y.data_ptr(), rows, cols // 256, stream))]
+            if knd == 6:
+                variants.append(("limb records + residual", lambda c: lib.mg_matvec_kquant_on_stream(
+                    14, w.data_ptr() + c * one.size, rec.data_ptr(), 1, y.data_ptr(), y.data_ptr(), rows, cols // 256, stream)))
+            for vname, fn in variants:
+                for i in range(5):
+                    assert fn(i % copies) == 0
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 40
+                a.record()
+                for i in range(reps):
+                    fn(i % copies)
+                b.record()
+                torch.cuda.synchronize()
+                us = a.elapsed_time(b) / reps * 1e3
+                nbytes = rows * (cols // 256) * block_bytes[knd] + 4 * cols + 4 * rows
+                shapes.append({"type": name, "tensor": label, "rows": rows, "cols": cols, "input": vname,
+                               "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+                               "hbm_frac": round(nbytes / us / 1e3 / peak, 4)})
+            del w
+    out = {"matvec": shapes, "peak_source": f"of {kind}", "gpu_launches": len(shapes) * 40}
+    if args.kquant_no_decode:
+        return out
+    torch.cuda.empty_cache()
+    cfg = dec.QWEN25_7B
+    Q4, Q6, F16 = 12, 14, 1
+    n = cfg.n_layers
+    more_bits = lambda l: l < n // 8 or l >= 7 * n // 8 or (l - n // 8) % 3 == 2
+    mix = [[Q4, Q4, Q6 if more_bits(l) else Q4, Q4, Q4, Q4, Q6 if more_bits(l) else Q4] for l in range(n)]
+    d = dec.Q4KDecoder(cfg, types=(mix, Q4, Q6))
+    D = cfg.d_model
+
+    def mat(t, r, c):
+        return synth.q4k_matrix(r, c, rng) if t == Q4 else synth.kquant_matrix(6, r, c, rng)
+
+    total = 0
+    for which, t in ((dec.W_EMBED, Q4), (dec.W_LM_HEAD, Q6)):
+        m = mat(t, cfg.vocab, D)
+        total += m.size if which == dec.W_LM_HEAD else D // 256 * 144
+        d.upload(0, which, m)
+    norm = (1.0 + 0.05 * rng.standard_normal(D, dtype=np.float32)).astype(np.float32)
+    d.upload(0, dec.W_OUT_NORM, norm)
+    for l in range(n):
+        for idx, (o, i_) in enumerate(cfg.shapes().values()):
+            m = mat(mix[l][idx], o, i_)
+            total += m.size
+            d.upload(l, idx, m)
+        d.upload(l, dec.W_ATTN_NORM, norm)
+        d.upload(l, dec.W_FFN_NORM, norm)
+        k = rng.standard_normal(args.decode_prefill * cfg.kv_dim, dtype=np.float32).astype(np.float16)
+        d.set_kv(l, k, k, args.decode_prefill)
+    d.generate(1, 4)                       # graph capture + warm-up
+    d.set_position(args.decode_prefill)
+    tokens = min(args.decode_tokens, 128)
+    _, ms = d.generate(1, tokens)
+    ms_tok = ms / tokens
+    kv = 2 * n * cfg.kv_dim * 2 * (args.decode_prefill + tokens // 2)
+    out["decode_mixed"] = {"tok_s": round(1e3 / ms_tok, 2), "ms_per_token": round(ms_tok, 4), "tokens": tokens,
+                           "weight_bytes_per_token": total, "gbs": round((total + kv) / ms_tok / 1e6, 1),
+                           "hbm_frac": round((total + kv) / ms_tok / 1e6 / peak, 4),
+                           "launches_per_token": d.kernels_per_token(),
+                           "model": "qwen2.5-7b-shaped, random-init; attn_v and ffn_down Q6_K in %d of %d layers, "
+                                    "Q4_K embedding, Q6_K LM head, other linears Q4_K" % (sum(map(more_bits, range(n))), n)}
     d.close()
     return out
 
