@@ -815,8 +815,8 @@ def decode_leg(args):
 def kquant_leg(args, torch, lib, dev):
     """The other K-quants of a real checkpoint.  (1) Q5_K / Q6_K batch-1 matvecs on the 7B shapes where such
     tensors occur (attn_v, ffn_down, the LM head), weights rotated through > 400 MB of copies, CUDA events
-    around back-to-back launches; Q6_K also from limb records with the residual add folded in, as the typed
-    engine calls it.  (2) Greedy decode of the 7B-class model with the tensor types of a Q4_K_M-style file:
+    around back-to-back launches, from f32 activations and from limb records with the residual add folded in
+    (as the typed engine calls them).  (2) Greedy decode of the 7B-class model with the tensor types of a Q4_K_M-style file:
     attn_v and ffn_down Q6_K in half of the layers, Q4_K token embedding, Q6_K LM head, the rest Q4_K."""
     from modgrad_b200 import decoder as dec
     rng = np.random.Generator(np.random.PCG64(77))
@@ -836,9 +836,8 @@ def kquant_leg(args, torch, lib, dev):
             assert lib.mg_q4k_x_to_limbs_on_stream(x.data_ptr(), cols, rec.data_ptr(), stream) == 0
             variants = [("f32 x", lambda c: lib.mg_matvec_kquant_on_stream(8 + knd, w.data_ptr() + c * one.size, x.data_ptr(), 0,
                                                                            None, y.data_ptr(), rows, cols // 256, stream))]
-            if knd == 6:
-                variants.append(("limb records + residual", lambda c: lib.mg_matvec_kquant_on_stream(
-                    14, w.data_ptr() + c * one.size, rec.data_ptr(), 1, y.data_ptr(), y.data_ptr(), rows, cols // 256, stream)))
+            variants.append(("limb records + residual", lambda c: lib.mg_matvec_kquant_on_stream(
+                8 + knd, w.data_ptr() + c * one.size, rec.data_ptr(), 1, y.data_ptr(), y.data_ptr(), rows, cols // 256, stream)))
             for vname, fn in variants:
                 for i in range(5):
                     assert fn(i % copies) == 0

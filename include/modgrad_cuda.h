@@ -96,12 +96,14 @@ int launch_matvec_q6k_on_stream(const uint8_t* w_q6, const float* x, float* y, i
                                 void* stream);
 /* y[row] = (add ? add[row] : 0) + W[row] . x for a Q5_K (ggml_type 13) or Q6_K (14) weight: the matvec with
  * the residual add the decode loop puts behind it (crates/modgrad-gemma/src/rocm_gemma.rs:470-475, :497-500)
- * folded in; y may alias add.  x_kind 0: x is the f32 activation vector.  x_kind 1 (Q6_K only, weight
- * 4-byte aligned, blocks_per_row * 832 bytes within one CTA's shared memory): x holds the limb records of
- * mg_q4k_x_to_limbs_on_stream / mg_swiglu_limbs_on_stream, multiplied with dp4a.  launch_matvec_q6k takes
- * the same integer path for rows of up to 32 blocks (it converts x itself) when the weight is 4-byte
- * aligned: the result then carries the activations' rounding to 23 bits of each 32-element sub-block's
- * largest element, like the Q4_K launchers'. */
+ * folded in; y may alias add.  x_kind 0: x is the f32 activation vector.  x_kind 1 (weight 4-byte aligned,
+ * blocks_per_row * 832 bytes (+ 12 KiB for few or long rows) within one CTA's shared memory): x holds the limb
+ * records of mg_q4k_x_to_limbs_on_stream / mg_swiglu_limbs_on_stream, multiplied with dp4a.
+ * launch_matvec_q5k / launch_matvec_q6k take the same integer path under the same conditions (they convert x
+ * themselves): the result then carries the activations' rounding to 23 bits of each 32-element sub-block's
+ * largest element, like the Q4_K launchers'; otherwise a float kernel runs.  The kernels request their
+ * first weights before they wait for the previous kernel of the stream: the weight must not be produced by
+ * the kernel launched immediately before on the same stream. */
 int mg_matvec_kquant_on_stream(int ggml_type, const uint8_t* w, const void* x, int x_kind, const float* add, float* y,
                                int out_dim, int blocks_per_row, void* stream);
 int launch_matvec_q6k_dp4a(const uint8_t* w, const int8_t* xq, const float* xd, const float* xsum, float* y,

@@ -509,10 +509,10 @@ int queue_token_mixed(mg_decoder* d) {
             const int rows[1] = {D};
             if ((e = mg_matvec_q4k_multi_on_stream(1, w, d->records, 1, add, y, rows, F / 256, s))) return fail(d, e, "down");
             d->mixed_launches += 2;
-        } else if (L.type[6] == kTypeQ6K && (size_t)(F / 256) * 4 * 208 <= (size_t)200 * 1024) {
-            // Q6_K takes the same limb records (while they fit one CTA's shared memory)
+        } else if ((size_t)(F / 256) * 4 * 208 <= (size_t)200 * 1024) {
+            // Q5_K / Q6_K take the same limb records (while they fit one CTA's shared memory)
             if ((e = mg_swiglu_limbs_on_stream(d->gate, d->up, nullptr, F, d->records, s))) return fail(d, e, "swiglu");
-            if ((e = mg_matvec_kquant_on_stream(kTypeQ6K, L.wdown, d->records, 1, d->hidden, d->hidden, D, F / 256, s)))
+            if ((e = mg_matvec_kquant_on_stream(L.type[6], L.wdown, d->records, 1, d->hidden, d->hidden, D, F / 256, s)))
                 return fail(d, e, "down");
             d->mixed_launches += 2;
         } else {

@@ -303,25 +303,31 @@ __device__ __forceinline__ uint32_t q6_signed4(uint32_t lo, uint32_t h) {
     return (q ^ 0x20202020u) + neg * 6u;                  // bit 5 flipped, bits 6 and 7 set where negative
 }
 
-// The 32 weights of lane (G, qtr) in one block, still packed, with their four scale bytes and d.
-struct Q6Lane {
-    uint2 ql0, ql1, qh;
-    int sc[4];
-    uint32_t d_bits;
-};
-__device__ __forceinline__ void q6_load(Q6Lane& t, const uint8_t* b, int G, int qtr) {
-    t.ql0 = ld8_align2(b + 64 * G + 8 * qtr);
-    t.ql1 = ld8_align2(b + 64 * G + 32 + 8 * qtr);
-    t.qh = ld8_align2(b + 128 + 32 * G + 8 * qtr);
-    const int8_t* s8 = reinterpret_cast<const int8_t*>(b + 192 + 8 * G + (qtr >> 1));
+// A format for the limb kernels: the packed weights one lane keeps of one block (Lane), their loads, and
+// the R rows' dot products with block `blk` of the activations.  `sub` = lane & 7: eight lanes cover a block.
+//
+// Q6_K: lane (G = sub / 4, qtr = sub % 4) owns columns 8 qtr .. 8 qtr + 7 of the four 32-column groups of half G.
+struct Q6Fmt {
+    static constexpr int kBytes = kQ6Bytes;
+    struct Lane {
+        uint2 ql0, ql1, qh;
+        int sc[4];
+        uint32_t d_bits;
+    };
+    static __device__ __forceinline__ void load(Lane& t, const uint8_t* b, int sub) {
+        const int G = sub >> 2, qtr = sub & 3;
+        t.ql0 = ld8_align2(b + 64 * G + 8 * qtr);
+        t.ql1 = ld8_align2(b + 64 * G + 32 + 8 * qtr);
+        t.qh = ld8_align2(b + 128 + 32 * G + 8 * qtr);
+        const int8_t* s8 = reinterpret_cast<const int8_t*>(b + 192 + 8 * G + (qtr >> 1));
 #pragma unroll
-    for (int k = 0; k < 4; ++k) t.sc[k] = (int)s8[2 * k];
-    t.d_bits = *reinterpret_cast<const uint16_t*>(b + 208);
-}
-// R rows' dot products with block `blk` of the activations: acc[r] += d_r * sum_k sc_rk * s_k * <q_rk, a_k>.
-// rec_w: the limb records of the whole vector.
-template <int R>
-__device__ __forceinline__ void q6_dot(const Q6Lane (&t)[R], const uint32_t* rec_w, int blk, int G, int qtr, float (&acc)[R]) {
+        for (int k = 0; k < 4; ++k) t.sc[k] = (int)s8[2 * k];
+        t.d_bits = *reinterpret_cast<const uint16_t*>(b + 208);
+    }
+    // acc[r] += d_r * sum_k sc_rk * s_k * <q_rk, a_k>;  rec_w: the limb records of the whole vector
+    template <int R>
+    static __device__ __forceinline__ void dot(const Lane (&t)[R], const uint32_t* rec_w, int blk, int sub, float (&acc)[R]) {
+        const int G = sub >> 2, qtr = sub & 3;
     float part[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) part[r] = 0.0f;
@@ -352,12 +358,67 @@ __device__ __forceinline__ void q6_dot(const Q6Lane (&t)[R], const uint32_t* rec
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) acc[r] = fmaf(q4k::half_bits_finite_or_zero(t[r].d_bits), part[r], acc[r]);
-}
+    }
+};
+
+// Q5_K: lane (g = sub / 2, half = sub % 2) owns columns 16 half .. 16 half + 15 of both 32-column sub-blocks of
+// quant group g: 16 `ql` bytes (low nibbles: sub-block 2g, high: 2g + 1), the 16 `qh` bytes of those columns
+// (bit 2g + hi of each) and the header, three 16-byte loads (blocks are 16-byte aligned).  The quants stay
+// unsigned; the minimum enters once per sub-block through the record's s * sum(a) word, added by half 0.
+struct Q5Fmt {
+    static constexpr int kBytes = kQ5Bytes;
+    struct Lane {
+        uint4 hdr, ql, qh;
+    };
+    static __device__ __forceinline__ void load(Lane& t, const uint8_t* b, int sub) {
+        const int g = sub >> 1, half = sub & 1;
+        t.hdr = q4k::ld_nc_u4(b);
+        t.qh = q4k::ld_nc_u4(b + 16 + 16 * half);
+        t.ql = q4k::ld_nc_u4(b + 48 + 32 * g + 16 * half);
+    }
+    template <int R>
+    static __device__ __forceinline__ void dot(const Lane (&t)[R], const uint32_t* rec_w, int blk, int sub, float (&acc)[R]) {
+        const int g = sub >> 1, half = sub & 1;
+        const uint32_t* rp = rec_w + (size_t)(blk * 4 + g) * xlimbs::kRecordWords;
+#pragma unroll
+        for (int hi = 0; hi < 2; ++hi) {
+            // activations of sub-block 2g + hi: plane set hi of record g, words 4 half .. 4 half + 3
+            const uint32_t* lp = rp + hi * 24 + 4 * half;
+            const uint4 a2 = *reinterpret_cast<const uint4*>(lp);
+            const uint4 a1 = *reinterpret_cast<const uint4*>(lp + 8);
+            const uint4 a0 = *reinterpret_cast<const uint4*>(lp + 16);
+            const float s = __uint_as_float(rp[48 + hi]);
+            const float sx = half == 0 ? __uint_as_float(rp[50 + hi]) : 0.0f;   // s * sum(a) of the whole sub-block
+            const int bit = 2 * g + hi;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint32_t v[4] = {t[r].ql.x, t[r].ql.y, t[r].ql.z, t[r].ql.w};
+                const uint32_t h[4] = {t[r].qh.x, t[r].qh.y, t[r].qh.z, t[r].qh.w};
+                const uint32_t l2[4] = {a2.x, a2.y, a2.z, a2.w}, l1[4] = {a1.x, a1.y, a1.z, a1.w}, l0[4] = {a0.x, a0.y, a0.z, a0.w};
+                int i2 = 0;
+                uint32_t i1 = 0, i0 = 0;
+#pragma unroll
+                for (int wd = 0; wd < 4; ++wd) {
+                    const uint32_t q = ((hi ? v[wd] >> 4 : v[wd]) & 0x0F0F0F0Fu) | (((h[wd] >> bit) & 0x01010101u) << 4);   // 0..31
+                    i2 = gemvdev::dp4a_us(q, l2[wd], i2);
+                    i1 = gemvdev::dp4a_uu(q, l1[wd], i1);
+                    i0 = gemvdev::dp4a_uu(q, l0[wd], i0);
+                }
+                // |i2| < 2^15, i1 and i0 < 2^17: the conversions are exact, the two fused adds round
+                const float f = fmaf((float)i2, 65536.0f, fmaf((float)i1, 256.0f, (float)i0));
+                const float d = q4k::half_bits_finite_or_zero(t[r].hdr.x), dmin = q4k::half_bits_finite_or_zero(t[r].hdr.x >> 16);
+                const q4k::ScaleMin sm = q4k::unpack_scales(t[r].hdr.y, t[r].hdr.z, t[r].hdr.w);
+                const float dsc = d * (float)q4k::scale_of(sm, bit), dm = dmin * (float)q4k::min_of(sm, bit);
+                acc[r] = fmaf(dsc, f * s, fmaf(-dm, sx, acc[r]));
+            }
+        }
+    }
+};
 
 // The activation vector as limb records in shared memory.  FROM_X = 1: src is the f32 vector, converted
 // here; 0: src holds records (mg_q4k_x_to_limbs_on_stream, mg_swiglu_limbs_on_stream).
 template <int FROM_X, int THREADS>
-__device__ __forceinline__ void q6_stage_records(const void* src, int bpr, int x_aligned, uint4* rec_s) {
+__device__ __forceinline__ void limbs_stage_records(const void* src, int bpr, int x_aligned, uint4* rec_s) {
     if (FROM_X) {
         const float* x = static_cast<const float*>(src);
         const int n_chunks = bpr * 64;   // a multiple of 64: warps are whole
@@ -375,23 +436,22 @@ __device__ __forceinline__ void q6_stage_records(const void* src, int bpr, int x
     __syncthreads();
 }
 
-constexpr int kQ6LimbThreads = 256, kQ6LimbWarps = kQ6LimbThreads / 32;
+constexpr int kLimbThreads = 256, kLimbWarps = kLimbThreads / 32;
 
 // Short rows, many of them: a warp owns R rows at a time and walks their blocks four per step.
 // y[row] = (add ? add[row] : 0) + W[row] . x.
-template <int R, int FROM_X>
-__global__ void __launch_bounds__(kQ6LimbThreads, 4) matvec_q6k_limbs_kernel(const uint8_t* __restrict__ w, const void* src,
-                                                                          const float* add, float* y, int out_dim, int bpr,
-                                                                          int x_aligned) {
+template <class FMT, int R, int FROM_X>
+__device__ __forceinline__ void limbs_short_body(const uint8_t* __restrict__ w, const void* src, const float* add, float* y,
+                                                 int out_dim, int bpr, int x_aligned) {
     extern __shared__ __align__(16) uint4 rec_s[];
     const uint32_t* rec_w = reinterpret_cast<const uint32_t*>(rec_s);
     mg::pdl_prologue();
-    q6_stage_records<FROM_X, kQ6LimbThreads>(src, bpr, x_aligned, rec_s);
+    limbs_stage_records<FROM_X, kLimbThreads>(src, bpr, x_aligned, rec_s);
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int bsel = lane >> 3, G = (lane >> 2) & 1, qtr = lane & 3;
-    const size_t row_bytes = (size_t)bpr * kQ6Bytes;
-    for (int row0 = (blockIdx.x * kQ6LimbWarps + warp) * R; row0 < out_dim; row0 += gridDim.x * kQ6LimbWarps * R) {
+    const int bsel = lane >> 3, sub = lane & 7;
+    const size_t row_bytes = (size_t)bpr * FMT::kBytes;
+    for (int row0 = (blockIdx.x * kLimbWarps + warp) * R; row0 < out_dim; row0 += gridDim.x * kLimbWarps * R) {
         float acc[R];
         const uint8_t* wr[R];
 #pragma unroll
@@ -400,10 +460,10 @@ __global__ void __launch_bounds__(kQ6LimbThreads, 4) matvec_q6k_limbs_kernel(con
             wr[r] = w + (size_t)min(row0 + r, out_dim - 1) * row_bytes;   // a row past the end repeats the last one
         }
         for (int blk = bsel; blk < bpr; blk += 4) {
-            Q6Lane t[R];
+            typename FMT::Lane t[R];
 #pragma unroll
-            for (int r = 0; r < R; ++r) q6_load(t[r], wr[r] + (size_t)blk * kQ6Bytes, G, qtr);
-            q6_dot<R>(t, rec_w, blk, G, qtr, acc);
+            for (int r = 0; r < R; ++r) FMT::load(t[r], wr[r] + (size_t)blk * FMT::kBytes, sub);
+            FMT::template dot<R>(t, rec_w, blk, sub, acc);
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -412,61 +472,72 @@ __global__ void __launch_bounds__(kQ6LimbThreads, 4) matvec_q6k_limbs_kernel(con
         }
     }
 }
+template <int R, int FROM_X>
+__global__ void __launch_bounds__(kLimbThreads, 4) matvec_q6k_limbs_kernel(const uint8_t* __restrict__ w, const void* src,
+                                                                           const float* add, float* y, int out_dim, int bpr,
+                                                                           int x_aligned) {
+    limbs_short_body<Q6Fmt, R, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned);
+}
+template <int R, int FROM_X>
+__global__ void __launch_bounds__(kLimbThreads, 3) matvec_q5k_limbs_kernel(const uint8_t* __restrict__ w, const void* src,
+                                                                           const float* add, float* y, int out_dim, int bpr,
+                                                                           int x_aligned) {
+    limbs_short_body<Q5Fmt, R, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned);
+}
 
 // Long rows, few of them (a down projection): one CTA per SM keeps the records (one copy per SM, not
 // per small CTA) and takes an even share of the rows; its 96 eight-lane groups walk the (row, block)
 // pairs of up to 32 rows cyclically, so that every group has the same number of blocks whatever the
 // row length, and leave one partial sum per (row, group) in shared memory, summed in a fixed order.
-constexpr int kQ6LongThreads = 768, kQ6LongGroups = kQ6LongThreads / 8, kQ6LongRows = 32;
+constexpr int kLongThreads = 768, kLongGroups = kLongThreads / 8, kLongRows = 32;
 
-template <int FROM_X>
-__global__ void __launch_bounds__(kQ6LongThreads, 1) matvec_q6k_limbs_long_kernel(const uint8_t* __restrict__ w, const void* src,
-                                                                                  const float* add, float* y, int out_dim,
-                                                                                  int bpr, int x_aligned) {
+template <class FMT, int FROM_X>
+__device__ __forceinline__ void limbs_long_body(const uint8_t* __restrict__ w, const void* src, const float* add, float* y,
+                                                int out_dim, int bpr, int x_aligned) {
     extern __shared__ __align__(16) uint4 rec_s[];
     const uint32_t* rec_w = reinterpret_cast<const uint32_t*>(rec_s);
-    float* part = reinterpret_cast<float*>(rec_s + (size_t)bpr * 4 * xlimbs::kRecordVec4);   // [kQ6LongRows][kQ6LongGroups]
+    float* part = reinterpret_cast<float*>(rec_s + (size_t)bpr * 4 * xlimbs::kRecordVec4);   // [kLongRows][kLongGroups]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int group = threadIdx.x >> 3, G = (lane >> 2) & 1, qtr = lane & 3;
+    const int group = threadIdx.x >> 3, sub = lane & 7;
     const unsigned gmask = 0xFFu << (lane & 24);   // the eight lanes of this group
-    const size_t row_bytes = (size_t)bpr * kQ6Bytes;
+    const size_t row_bytes = (size_t)bpr * FMT::kBytes;
     const int row_begin = (int)((long long)blockIdx.x * out_dim / gridDim.x);
     const int row_end = (int)((long long)(blockIdx.x + 1) * out_dim / gridDim.x);
-    const int step_rows = kQ6LongGroups / bpr, step_blks = kQ6LongGroups - step_rows * bpr;   // one stride of a group
+    const int step_rows = kLongGroups / bpr, step_blks = kLongGroups - step_rows * bpr;   // one stride of a group
     // The weights do not depend on the kernel before this one: the first block is requested before the
     // wait for the activations, the next one always before the current one is multiplied.
-    Q6Lane nxt[1];
-    if (group < min(kQ6LongRows, row_end - row_begin) * bpr)
-        q6_load(nxt[0], w + (size_t)row_begin * row_bytes + (size_t)group * kQ6Bytes, G, qtr);
+    typename FMT::Lane nxt[1];
+    if (group < min(kLongRows, row_end - row_begin) * bpr)
+        FMT::load(nxt[0], w + (size_t)row_begin * row_bytes + (size_t)group * FMT::kBytes, sub);
     mg::pdl_prologue();
-    q6_stage_records<FROM_X, kQ6LongThreads>(src, bpr, x_aligned, rec_s);
+    limbs_stage_records<FROM_X, kLongThreads>(src, bpr, x_aligned, rec_s);
 
-    for (int pass0 = row_begin; pass0 < row_end; pass0 += kQ6LongRows) {
-        const int n_rows = min(kQ6LongRows, row_end - pass0);
-        for (int i = threadIdx.x; i < kQ6LongRows * kQ6LongGroups; i += kQ6LongThreads) part[i] = 0.0f;
+    for (int pass0 = row_begin; pass0 < row_end; pass0 += kLongRows) {
+        const int n_rows = min(kLongRows, row_end - pass0);
+        for (int i = threadIdx.x; i < kLongRows * kLongGroups; i += kLongThreads) part[i] = 0.0f;
         __syncthreads();
         const int n_items = n_rows * bpr;
         int cur = -1;
         float acc[1] = {0.0f};
         const uint8_t* wp = w + (size_t)pass0 * row_bytes;   // rows of a pass are one contiguous run of blocks
-        if (pass0 != row_begin && group < n_items) q6_load(nxt[0], wp + (size_t)group * kQ6Bytes, G, qtr);
+        if (pass0 != row_begin && group < n_items) FMT::load(nxt[0], wp + (size_t)group * FMT::kBytes, sub);
         int rl = group / bpr, blk = group - rl * bpr;   // (row, block) of item j
-        for (int j = group; j < n_items; j += kQ6LongGroups) {
+        for (int j = group; j < n_items; j += kLongGroups) {
             if (rl != cur) {   // the whole group moves on together
                 if (cur >= 0) {
                     float v = acc[0];
                     v += __shfl_xor_sync(gmask, v, 4);
                     v += __shfl_xor_sync(gmask, v, 2);
                     v += __shfl_xor_sync(gmask, v, 1);
-                    if ((lane & 7) == 0) part[cur * kQ6LongGroups + group] = v;
+                    if (sub == 0) part[cur * kLongGroups + group] = v;
                 }
                 cur = rl;
                 acc[0] = 0.0f;
             }
-            Q6Lane now[1];
+            typename FMT::Lane now[1];
             now[0] = nxt[0];
-            if (j + kQ6LongGroups < n_items) q6_load(nxt[0], wp + (size_t)(j + kQ6LongGroups) * kQ6Bytes, G, qtr);
-            q6_dot<1>(now, rec_w, blk, G, qtr, acc);
+            if (j + kLongGroups < n_items) FMT::load(nxt[0], wp + (size_t)(j + kLongGroups) * FMT::kBytes, sub);
+            FMT::template dot<1>(now, rec_w, blk, sub, acc);
             rl += step_rows;
             blk += step_blks;
             if (blk >= bpr) { blk -= bpr; ++rl; }
@@ -476,17 +547,29 @@ __global__ void __launch_bounds__(kQ6LongThreads, 1) matvec_q6k_limbs_long_kerne
             v += __shfl_xor_sync(gmask, v, 4);
             v += __shfl_xor_sync(gmask, v, 2);
             v += __shfl_xor_sync(gmask, v, 1);
-            if ((lane & 7) == 0) part[cur * kQ6LongGroups + group] = v;
+            if (sub == 0) part[cur * kLongGroups + group] = v;
         }
         __syncthreads();
-        for (int rr = warp; rr < n_rows; rr += kQ6LongThreads / 32) {
-            const float* pr = part + rr * kQ6LongGroups;
+        for (int rr = warp; rr < n_rows; rr += kLongThreads / 32) {
+            const float* pr = part + rr * kLongGroups;
             float t = (pr[lane] + pr[32 + lane]) + pr[64 + lane];
             t = q4k::warp_sum(t);
             if (lane == 0) y[pass0 + rr] = add ? add[pass0 + rr] + t : t;
         }
         __syncthreads();   // before the partial sums are cleared for the next rows
     }
+}
+template <int FROM_X>
+__global__ void __launch_bounds__(kLongThreads, 1) matvec_q6k_limbs_long_kernel(const uint8_t* __restrict__ w, const void* src,
+                                                                                const float* add, float* y, int out_dim,
+                                                                                int bpr, int x_aligned) {
+    limbs_long_body<Q6Fmt, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned);
+}
+template <int FROM_X>
+__global__ void __launch_bounds__(kLongThreads, 1) matvec_q5k_limbs_long_kernel(const uint8_t* __restrict__ w, const void* src,
+                                                                                const float* add, float* y, int out_dim,
+                                                                                int bpr, int x_aligned) {
+    limbs_long_body<Q5Fmt, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned);
 }
 
 // Q6_K weights x int8 activations (xq / xd / xsum from launch_quantize_q8_1):
@@ -548,67 +631,73 @@ int launch_matvec(const uint8_t* w, const float* x, const float* add, float* y, 
 
 // Few rows per SM (one pass of the long kernel), or rows of more than 32 blocks: the kernel that splits
 // the rows' blocks over a whole CTA.  Many short rows: a warp per pair of rows.
-bool q6_long_shape(int out_dim, int bpr) {
+bool limbs_long_shape(int out_dim, int bpr) {
     const mg::DeviceProps& dp = mg::device_props();
-    return bpr > 32 || out_dim <= (dp.ok ? dp.sm_count : 148) * kQ6LongRows;
+    return bpr > 32 || out_dim <= (dp.ok ? dp.sm_count : 148) * kLongRows;
 }
 
-// The limb kernels need the weight 4-byte aligned (their 8-byte loads round the address down) and the
-// whole activation vector as records in one CTA's shared memory.
-size_t q6_smem_bytes(int out_dim, int bpr) {
+// The limb kernels need the whole activation vector as records in one CTA's shared memory, and a Q6_K
+// weight 4-byte aligned (its 8-byte loads round the address down; Q5_K is 16-byte aligned by contract).
+size_t limbs_smem_bytes(int out_dim, int bpr) {
     return (size_t)bpr * 4 * xlimbs::kRecordBytes +
-           (q6_long_shape(out_dim, bpr) ? (size_t)kQ6LongRows * kQ6LongGroups * sizeof(float) : 0);
+           (limbs_long_shape(out_dim, bpr) ? (size_t)kLongRows * kLongGroups * sizeof(float) : 0);
 }
-bool q6_limbs_ok(const uint8_t* w, int out_dim, int bpr) {
+bool limbs_ok(const uint8_t* w, int out_dim, int bpr) {
     const mg::DeviceProps& dp = mg::device_props();
-    return (reinterpret_cast<uintptr_t>(w) & 3u) == 0 && dp.ok && q6_smem_bytes(out_dim, bpr) <= (size_t)dp.max_smem_optin;
+    return (reinterpret_cast<uintptr_t>(w) & 3u) == 0 && dp.ok && limbs_smem_bytes(out_dim, bpr) <= (size_t)dp.max_smem_optin;
 }
 
 template <class Kernel>
-int q6_allow_smem(Kernel kernel, size_t smem, size_t& configured) {
-    if (smem <= 48 * 1024 || smem <= configured) return 0;
-    const mg::DeviceProps& dp = mg::device_props();
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.max_smem_optin);
-    if (e != cudaSuccess) return (int)e;
-    configured = (size_t)dp.max_smem_optin;
-    return 0;
+int launch_limbs_kernel(Kernel kernel, size_t& configured, unsigned grid, int threads, size_t smem, const uint8_t* w,
+                        const void* src, const float* add, float* y, int out_dim, int bpr, void* stream) {
+    if (smem > 48 * 1024 && smem > configured) {   // configured: the largest dynamic shared memory set for this kernel
+        const mg::DeviceProps& dp = mg::device_props();
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.max_smem_optin);
+        if (e != cudaSuccess) return (int)e;
+        configured = (size_t)dp.max_smem_optin;
+    }
+    return (int)mg::launch_pdl(kernel, dim3(grid), dim3((unsigned)threads), smem, (cudaStream_t)stream, w, src, add, y, out_dim,
+                               bpr, mg::aligned16(src) ? 1 : 0);
 }
 
-template <int FROM_X>
-int launch_q6_limbs(const uint8_t* w, const void* src, const float* add, float* y, int out_dim, int bpr, void* stream) {
+template <int KIND, int FROM_X>
+int launch_limbs(const uint8_t* w, const void* src, const float* add, float* y, int out_dim, int bpr, void* stream) {
     const mg::DeviceProps& dp = mg::device_props();
-    const size_t smem = q6_smem_bytes(out_dim, bpr);
-    const int x_aligned = mg::aligned16(src) ? 1 : 0;
-    if (q6_long_shape(out_dim, bpr)) {
-        static size_t configured = 0;   // the largest dynamic shared memory the kernel was configured for
-        if (int rc = q6_allow_smem(matvec_q6k_limbs_long_kernel<FROM_X>, smem, configured)) return rc;
-        const int grid = out_dim < dp.sm_count ? out_dim : dp.sm_count;
-        return (int)mg::launch_pdl(matvec_q6k_limbs_long_kernel<FROM_X>, dim3((unsigned)grid), dim3(kQ6LongThreads), smem,
-                                   (cudaStream_t)stream, w, src, add, y, out_dim, bpr, x_aligned);
+    const size_t smem = limbs_smem_bytes(out_dim, bpr);
+    if (limbs_long_shape(out_dim, bpr)) {
+        static size_t configured = 0;
+        const unsigned grid = (unsigned)(out_dim < dp.sm_count ? out_dim : dp.sm_count);
+        if (KIND == 5)
+            return launch_limbs_kernel(matvec_q5k_limbs_long_kernel<FROM_X>, configured, grid, kLongThreads, smem, w, src, add, y,
+                                       out_dim, bpr, stream);
+        return launch_limbs_kernel(matvec_q6k_limbs_long_kernel<FROM_X>, configured, grid, kLongThreads, smem, w, src, add, y,
+                                   out_dim, bpr, stream);
     }
     constexpr int R = 2;
     static size_t configured = 0;
-    if (int rc = q6_allow_smem(matvec_q6k_limbs_kernel<R, FROM_X>, smem, configured)) return rc;
     // CTAs an SM holds: by shared memory (1 KiB reserved per CTA) and by threads
     int per_sm = (int)((228u * 1024u) / (smem + 1024));
-    per_sm = per_sm > 2048 / kQ6LimbThreads ? 2048 / kQ6LimbThreads : (per_sm < 1 ? 1 : per_sm);
-    int grid = (out_dim + R * kQ6LimbWarps - 1) / (R * kQ6LimbWarps);
+    per_sm = per_sm > 2048 / kLimbThreads ? 2048 / kLimbThreads : (per_sm < 1 ? 1 : per_sm);
+    int grid = (out_dim + R * kLimbWarps - 1) / (R * kLimbWarps);
     if (grid > dp.sm_count * per_sm) grid = dp.sm_count * per_sm;
-    return (int)mg::launch_pdl(matvec_q6k_limbs_kernel<R, FROM_X>, dim3((unsigned)grid), dim3(kQ6LimbThreads), smem,
-                               (cudaStream_t)stream, w, src, add, y, out_dim, bpr, x_aligned);
+    if (KIND == 5)
+        return launch_limbs_kernel(matvec_q5k_limbs_kernel<R, FROM_X>, configured, (unsigned)grid, kLimbThreads, smem, w, src, add,
+                                   y, out_dim, bpr, stream);
+    return launch_limbs_kernel(matvec_q6k_limbs_kernel<R, FROM_X>, configured, (unsigned)grid, kLimbThreads, smem, w, src, add, y,
+                               out_dim, bpr, stream);
 }
 
-// x_kind 0: f32 activations; 1: limb records (Q6_K only).
+// x_kind 0: f32 activations; 1: limb records.
 template <int KIND>
 int matvec_any(const uint8_t* w, const void* src, int x_kind, const float* add, float* y, int out_dim, int bpr, void* stream) {
     if (out_dim <= 0 || bpr <= 0 || !w || !src || !y || (x_kind != 0 && x_kind != 1)) return (int)cudaErrorInvalidValue;
-    if (KIND == 5 && (!mg::aligned16(w) || x_kind != 0)) return (int)cudaErrorInvalidValue;
+    if (KIND == 5 && !mg::aligned16(w)) return (int)cudaErrorInvalidValue;
     if (KIND == 6 && (reinterpret_cast<uintptr_t>(w) & 1u)) return (int)cudaErrorInvalidValue;
-    if (KIND == 6 && x_kind == 1) {
-        if (!q6_limbs_ok(w, out_dim, bpr) || !mg::aligned16(src)) return (int)cudaErrorInvalidValue;
-        return launch_q6_limbs<0>(w, src, add, y, out_dim, bpr, stream);
+    if (x_kind == 1) {
+        if (!limbs_ok(w, out_dim, bpr) || !mg::aligned16(src)) return (int)cudaErrorInvalidValue;
+        return launch_limbs<KIND, 0>(w, src, add, y, out_dim, bpr, stream);
     }
-    if (KIND == 6 && q6_limbs_ok(w, out_dim, bpr)) return launch_q6_limbs<1>(w, src, add, y, out_dim, bpr, stream);
+    if (limbs_ok(w, out_dim, bpr)) return launch_limbs<KIND, 1>(w, src, add, y, out_dim, bpr, stream);
     return launch_matvec<KIND>(w, static_cast<const float*>(src), add, y, out_dim, bpr, stream);
 }
 

@@ -77,9 +77,10 @@ def test_kquant_matvec(orc, cuda, kind, out_dim, bpr):
 
 
 @pytest.mark.parametrize("kind,out_dim,bpr,x_kind", [(6, 3584, 74, 1), (6, 3585, 14, 1), (6, 33, 3, 1), (6, 3584, 74, 0),
-                                                     (6, 640, 14, 0), (5, 3584, 74, 0), (5, 129, 14, 0)])
+                                                     (6, 640, 14, 0), (5, 3584, 74, 0), (5, 129, 14, 0), (5, 3584, 74, 1),
+                                                     (5, 3585, 14, 1), (5, 33, 3, 1), (5, 152064, 2, 1)])
 def test_kquant_matvec_with_residual_and_limb_records(orc, cuda, kind, out_dim, bpr, x_kind):
-    """mg_matvec_kquant_on_stream: y = add + W x in place, from f32 activations or (Q6_K) from limb records."""
+    """mg_matvec_kquant_on_stream: y = add + W x in place, from f32 activations or from limb records."""
     rng = np.random.Generator(np.random.PCG64(900 + out_dim + bpr + kind + x_kind))
     k = bpr * 256
     w = synth.kquant_matrix(kind, out_dim, k, rng)
@@ -118,18 +119,18 @@ def test_q6k_weight_that_is_only_two_byte_aligned(orc, cuda):
     rec = DeviceBuffer(cuda.mg_q4k_limb_record_bytes(bpr * 256))
     assert cuda.mg_q4k_x_to_limbs_on_stream(xd.ptr, bpr * 256, rec.ptr, None) == 0
     assert cuda.mg_matvec_kquant_on_stream(14, buf.ptr + 2, rec.ptr, 1, None, yd.ptr, out_dim, bpr, None) == 1
-    assert cuda.mg_matvec_kquant_on_stream(13, buf.ptr, rec.ptr, 1, None, yd.ptr, out_dim, bpr, None) == 1   # Q5_K: f32 only
     assert cuda.mg_matvec_kquant_on_stream(12, buf.ptr, xd.ptr, 0, None, yd.ptr, out_dim, bpr, None) == 1
     kern.sync()
 
 
-def test_q6k_non_finite_activation_poisons_every_row(cuda):
+@pytest.mark.parametrize("kind", [5, 6])
+def test_kquant_non_finite_activation_poisons_every_row(cuda, kind):
     out_dim, bpr = 64, 14
     rng = np.random.Generator(np.random.PCG64(94))
-    w = synth.kquant_matrix(6, out_dim, bpr * 256, rng)
+    w = synth.kquant_matrix(kind, out_dim, bpr * 256, rng)
     x = synth.activations(bpr * 256, rng)
     x[1000] = np.inf
-    y = gpu_matvec(cuda, 6, w, x, out_dim, bpr)
+    y = gpu_matvec(cuda, kind, w, x, out_dim, bpr)
     assert np.all(np.isnan(y))
 
 
