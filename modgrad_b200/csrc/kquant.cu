@@ -3,6 +3,9 @@
 //
 //   launch_matvec_q5k       replaces crates/modgrad-device/kernels/matvec_q5k.hip:55-121
 //   launch_matvec_q6k       replaces crates/modgrad-device/kernels/matvec_q6k.hip:32-94
+//   mg_matvec_kquant_on_stream: either of them with the residual add of the decode loop folded in, from f32
+//                           activations or from limb records
+//   mg_embed_kquant_on_stream: one row of a Q4_K / Q5_K / Q6_K embedding table, the token in device memory
 //   launch_matvec_q6k_dp4a  replaces crates/modgrad-device/kernels/matvec_q6k_dp4a.hip:56-150 (int8 activations
 //                           from launch_quantize_q8_1; lossy like its Q4_K sibling)
 //   mg_dequant_q5k / mg_dequant_q6k_on_stream: bulk dequantisation, bit-exact against the host
@@ -16,7 +19,9 @@
 //        (nibble (k >= 2) of ql[64G + 32(k&1) + l] | bits 2k,2k+1 of qh[32G + l] << 4) - 32, scale
 //        sc[8G + 2k + l/16];  w = fl(fl(d*sc) * q).  Rows are only 2-byte aligned (210 = 2 * 105).
 //
-// Matvec kernel shape (both formats): a CTA owns a few consecutive rows and its warps split the rows'
+// Matvecs: the limb kernels further down (integer dot products with dp4a on the activation records of
+// xlimbs.cuh) whenever the weight is 4-byte aligned and the records of a row fit one CTA's shared memory;
+// otherwise the float kernel: a CTA owns a few consecutive rows and its warps split the rows'
 // super-blocks, one block per warp and step; a lane owns adjacent columns of every quant group (packed
 // 32-bit loads for Q5_K, 16-bit for the 2-byte-aligned Q6_K), eight weights per lane and block, f32
 // accumulate, warp-shuffle then fixed-order cross-warp reduction.  The dequantisers keep one warp per
@@ -265,19 +270,20 @@ __global__ void __launch_bounds__(WARPS * 32) matvec_kquant_kernel(const uint8_t
     }
 }
 
-// ---- Q6_K on limb records -------------------------------------------------------------------------
+// ---- Q5_K / Q6_K on limb records ------------------------------------------------------------------
 // The float kernel above spends about 12 lane-operations per weight (a byte permute, a subtraction
 // and a multiply-add for each, plus the extraction) and is bound by instruction issue at a quarter of
-// the memory bandwidth.  This kernel multiplies the 6-bit quants with the activations in integers, as
-// the Q4_K kernels do (xlimbs.cuh): the activations are three byte limbs sharing one power-of-two
-// scale per 32 elements, the quants are sign-extended bytes, and eight weights meet their
-// activations in six dp4a.  The integer sums are exact; the result differs from the float kernel's by
-// the rounding of the activations to 23 bits of their sub-block's largest element.
+// the memory bandwidth.  These kernels multiply the quants with the activations in integers, as the
+// Q4_K kernels do (xlimbs.cuh): the activations are three byte limbs sharing one power-of-two scale
+// per 32 elements, the quants are bytes (Q6_K: sign-extended; Q5_K: unsigned, the minimum applied
+// through the records' sum word), and eight weights meet their activations in six dp4a.  The integer
+// sums are exact; the result differs from the float kernel's by the rounding of the activations to
+// 23 bits of their sub-block's largest element.
 //
-// A lane owns eight adjacent columns (qtr) of all four 32-column groups of one half (G) of a block:
-// 32 weights from six packed words, each group with its own scale byte and its own activation
-// sub-block.  Eight lanes cover a block, a warp four blocks per step and R rows at a time; every CTA
-// keeps the whole activation vector as limb records in shared memory.
+// Eight lanes cover a block, 32 weights each (the two formats split a block differently: Q6Fmt, Q5Fmt).
+// Two kernel bodies: a warp takes four blocks per step of R rows at a time (many short rows), or a
+// CTA per SM walks the (row, block) pairs of its rows with 96 eight-lane groups (few or long rows);
+// every CTA keeps the whole activation vector as limb records in shared memory.
 __device__ __forceinline__ int dp4a_su(uint32_t a_signed, uint32_t b_unsigned, int c) {
     int d;
     asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_signed), "r"(b_unsigned), "r"(c));
