@@ -298,14 +298,18 @@ enum {
 };
 typedef struct mg_decoder mg_decoder;
 int mg_decoder_create(const mg_decoder_config* cfg, mg_decoder** out);
-/* Single-GPU engine whose tensors carry their own GGUF types, as real checkpoints mix them: the
- * per-tensor dispatch of RocmGemma::qmatvec (crates/modgrad-gemma/src/rocm_gemma.rs:291-309).
- * proj_types: n_layers * 7 type ids in the order q, k, v, o, gate, up, down, each 12 (Q4_K), 13 (Q5_K)
- * or 14 (Q6_K); embed_type / head_type: 1 (F16) or one of the three.  mg_decoder_upload then expects
- * the byte size of each tensor's type; mg_decoder_weight_type reports it (0 for the f32 norms).
- * All-default types build the engine of mg_decoder_create. */
+/* Engine whose tensors carry their own GGUF types, as real checkpoints mix them: the per-tensor dispatch of
+ * RocmGemma::qmatvec (crates/modgrad-gemma/src/rocm_gemma.rs:291-309).  proj_types: n_layers * 7 type ids in
+ * the order q, k, v, o, gate, up, down, each 12 (Q4_K), 13 (Q5_K) or 14 (Q6_K); embed_type / head_type: 1 (F16)
+ * or one of the three.  mg_decoder_upload then expects the byte size of each tensor's type (of this rank's
+ * rows); mg_decoder_weight_type reports the type (0 for the f32 norms).  All-default types build the engine of
+ * mg_decoder_create[_sharded].  The _sharded form splits rows over the ranks exactly as
+ * mg_decoder_create_sharded does; a typed engine gathers with separate peer-store kernels or NCCL (the fused
+ * and stamped exchanges belong to the all-Q4_K engine). */
 int mg_decoder_create_typed(const mg_decoder_config* cfg, const int* proj_types, int embed_type, int head_type,
                             mg_decoder** out);
+int mg_decoder_create_typed_sharded(const mg_decoder_config* cfg, const int* proj_types, int embed_type, int head_type,
+                                    int rank, int world, const void* nccl_id128, mg_decoder** out);
 int mg_decoder_weight_type(const mg_decoder* d, int layer, int which);
 /* Row-sharded engine, one process per GPU (no counterpart in the reference, which has no
  * multi-device code): rank r of `world` holds the rows of its query heads, of its slice of

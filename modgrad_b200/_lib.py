@@ -97,6 +97,7 @@ SIGNATURES = {
     "mg_argmax_on_stream": (ci, [vp, ci, vp, vp, vp, vp, vp]),
     "mg_decoder_create": (ci, [vp, C.POINTER(vp)]),
     "mg_decoder_create_typed": (ci, [vp, vp, ci, ci, C.POINTER(vp)]),
+    "mg_decoder_create_typed_sharded": (ci, [vp, vp, ci, ci, ci, ci, vp, C.POINTER(vp)]),
     "mg_decoder_weight_type": (ci, [vp, ci, ci]),
     "mg_matvec_kquant_on_stream": (ci, [ci, vp, vp, ci, vp, vp, ci, ci, vp]),
     "mg_embed_kquant_on_stream": (ci, [vp, ci, ci, vp, vp, ci, ci, vp]),

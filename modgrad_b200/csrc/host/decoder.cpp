@@ -283,10 +283,10 @@ mgpeer::StampIn stamp_in(mg_decoder* d, int site, const unsigned long long* slot
 // kernels, which may start as soon as their predecessor lets its successor launch: there the
 // kernels that feed a collective keep their trigger until they have finished.
 int queue_token(mg_decoder* d) {
-    if (d->mixed) return queue_token_mixed(d);
-    if (d->world == 1 || d->peer) return queue_token_impl(d);  // the peer-store gathers are our own kernels
+    int (*impl)(mg_decoder*) = d->mixed ? queue_token_mixed : queue_token_impl;
+    if (d->world == 1 || d->peer) return impl(d);  // the peer-store gathers are our own kernels
     const int before = mg_pdl_early_trigger(0);
-    const int rc = queue_token_impl(d);
+    const int rc = impl(d);
     mg_pdl_early_trigger(before);
     return rc;
 }
@@ -452,14 +452,47 @@ int norm_project(mg_decoder* d, int n, const uint8_t* const* w, const uint8_t* t
     return 0;
 }
 
-// One token of an engine whose tensors are not all of the default types (single GPU): the same
-// arithmetic, queued through the launchers of each tensor's type.  A real checkpoint mixes Q4_K with
-// Q6_K (attn_v, ffn_down, token embedding, LM head) and Q5_K.
+// hidden += W x for one projection whose rows are split over the ranks: one GPU adds in place (the matvec
+// itself adds); a sharded rank writes its rows into `gathered`, the rows are all-gathered and a small
+// kernel adds the whole vector.  x_kind 0: f32 activations, 1: limb records.
+int project_add(mg_decoder* d, int type, const uint8_t* w, const void* x, int x_kind, float* gathered, int site, int cols,
+                const char* what) {
+    const int D = d->cfg.d_model;
+    const bool sharded = d->world > 1;
+    float* y = sharded ? gathered + (size_t)d->rank * d->d_loc : d->hidden;
+    const float* add = sharded ? nullptr : d->hidden;
+    int e;
+    if (type == kTypeQ4K) {
+        const uint8_t* ws[1] = {w};
+        float* ys[1] = {y};
+        const float* adds[1] = {add};
+        const int rows[1] = {d->d_loc};
+        e = mg_matvec_q4k_multi_on_stream(1, ws, x, x_kind, adds, ys, rows, cols / 256, d->stream);
+    } else {
+        e = mg_matvec_kquant_on_stream(type, w, x, x_kind, add, y, d->d_loc, cols / 256, d->stream);
+    }
+    if (e) return fail(d, e, what);
+    d->mixed_launches += 1;
+    if (sharded) {
+        if ((e = gather_equal(d, site, gathered, (size_t)d->d_loc, mgnccl::kFloat32, 4))) return e;
+        mg::launch_pdl(residual_add_kernel, dim3((D + 255) / 256), dim3(256), 0, d->stream, d->hidden, (const float*)gathered, D);
+        d->mixed_launches += 2;
+    }
+    return 0;
+}
+
+// One token of an engine whose tensors are not all of the default types: the same arithmetic, queued
+// through the launchers of each tensor's type.  A real checkpoint mixes Q4_K with Q6_K (attn_v, ffn_down,
+// token embedding, LM head) and Q5_K.  Row-sharded, the four exchanges of a layer are separate gathers
+// (peer-store gather kernels, or NCCL), not fused into the producing kernels.
 int queue_token_mixed(mg_decoder* d) {
     const mg_decoder_config& c = d->cfg;
     void* s = d->stream;
     const int D = c.d_model, hd = c.head_dim, F = c.d_ff;
-    const int q_dim = c.n_heads * hd, kv_dim = c.n_kv_heads * hd;
+    const int q_dim = c.n_heads * hd;
+    const int Hl = d->h1 - d->h0, KVl = d->kv1 - d->kv0;
+    const int q_loc = Hl * hd, kv_loc = KVl * hd;
+    const bool sharded = d->world > 1;
     const float scale = 1.0f / sqrtf((float)hd);
     int e;
     int* pos_dev = d->state;
@@ -470,61 +503,61 @@ int queue_token_mixed(mg_decoder* d) {
     else e = mg_embed_kquant_on_stream(d->embed, d->embed_type, 0, tok_dev, d->hidden, D, c.vocab, s);
     if (e) return fail(d, e, "embed");
     d->mixed_launches += 1;
+    // the SwiGLU output goes to limb records while a row of them fits one CTA's shared memory (always, sharded)
+    const bool records_fit = (size_t)(F / 256) * 4 * 208 <= (size_t)200 * 1024;
     for (int l = 0; l < c.n_layers; ++l) {
         const Layer& L = d->layers[l];
         {
             const uint8_t* w[3] = {L.wq, L.wk, L.wv};
             float* y[3] = {d->q, d->k, d->v};
-            const int rows[3] = {q_dim, kv_dim, kv_dim};
+            const int rows[3] = {q_loc, kv_loc, kv_loc};
             if ((e = norm_project(d, 3, w, L.type, L.attn_norm, y, rows, D, "qkv"))) return e;
         }
-        if ((e = mg_sdpa_rope_decode_f16kv_on_stream(d->q, d->k, d->v, L.k_cache, L.v_cache, d->att_full, c.n_heads,
-                                                     c.n_kv_heads, hd, 0, pos_dev, scale, c.rope_base, d->rope_freq,
-                                                     d->attn_scratch, d->n_splits, s)))
+        // this rank's heads land at their place in the full attention vector
+        if ((e = mg_sdpa_rope_decode_f16kv_on_stream(d->q, d->k, d->v, L.k_cache, L.v_cache, d->att_full + (size_t)d->h0 * hd, Hl,
+                                                     KVl, hd, 0, pos_dev, scale, c.rope_base, d->rope_freq, d->attn_scratch,
+                                                     d->n_splits, s)))
             return fail(d, e, "attention");
         d->mixed_launches += 1;
-        if (L.type[3] == kTypeQ4K) {   // hidden += Wo . att, added by the matvec itself
-            const uint8_t* w[1] = {L.wo};
-            float* y[1] = {d->hidden};
-            const float* add[1] = {d->hidden};
-            const int rows[1] = {D};
-            if ((e = mg_matvec_q4k_multi_on_stream(1, w, d->att_full, 0, add, y, rows, q_dim / 256, s))) return fail(d, e, "o_proj");
-            d->mixed_launches += 1;
-        } else {   // Q5_K / Q6_K: the same, the residual add folded into the matvec
-            if ((e = mg_matvec_kquant_on_stream(L.type[3], L.wo, d->att_full, 0, d->hidden, d->hidden, D, q_dim / 256, s)))
-                return fail(d, e, "o_proj");
-            d->mixed_launches += 1;
-        }
+        if ((e = gather_heads(d))) return e;
+        if ((e = project_add(d, L.type[3], L.wo, d->att_full, 0, d->tmp_full, kSiteOut, q_dim, "o_proj"))) return e;
         {
             const uint8_t* w[2] = {L.wgate, L.wup};
             float* y[2] = {d->gate, d->up};
-            const int rows[2] = {F, F};
+            const int rows[2] = {d->f_loc, d->f_loc};
             if ((e = norm_project(d, 2, w, L.type + 4, L.ffn_norm, y, rows, D, "gate_up"))) return e;
         }
-        if (L.type[6] == kTypeQ4K) {   // SwiGLU straight into limb records, hidden += Wdown . act in place
-            if ((e = mg_swiglu_limbs_on_stream(d->gate, d->up, nullptr, F, d->records, s))) return fail(d, e, "swiglu");
-            const uint8_t* w[1] = {L.wdown};
-            float* y[1] = {d->hidden};
-            const float* add[1] = {d->hidden};
-            const int rows[1] = {D};
-            if ((e = mg_matvec_q4k_multi_on_stream(1, w, d->records, 1, add, y, rows, F / 256, s))) return fail(d, e, "down");
-            d->mixed_launches += 2;
-        } else if ((size_t)(F / 256) * 4 * 208 <= (size_t)200 * 1024) {
-            // Q5_K / Q6_K take the same limb records (while they fit one CTA's shared memory)
-            if ((e = mg_swiglu_limbs_on_stream(d->gate, d->up, nullptr, F, d->records, s))) return fail(d, e, "swiglu");
-            if ((e = mg_matvec_kquant_on_stream(L.type[6], L.wdown, d->records, 1, d->hidden, d->hidden, D, F / 256, s)))
-                return fail(d, e, "down");
-            d->mixed_launches += 2;
-        } else {
+        if (L.type[6] == kTypeQ4K || records_fit) {
+            // SwiGLU straight into limb records (a rank's slice is a whole number of records), which the Q4_K,
+            // Q5_K and Q6_K down projections all read
+            uint8_t* rec = static_cast<uint8_t*>(d->records) + mg_q4k_limb_record_bytes(d->f_loc) * d->rank;
+            if ((e = mg_swiglu_limbs_on_stream(d->gate, d->up, nullptr, d->f_loc, rec, s))) return fail(d, e, "swiglu");
+            d->mixed_launches += 1;
+            if ((e = gather_equal(d, kSiteRecords, d->records, mg_q4k_limb_record_bytes(d->f_loc), mgnccl::kUint8, 1))) return e;
+            if ((e = project_add(d, L.type[6], L.wdown, d->records, 1, d->tmp_down, kSiteDown, F, "down"))) return e;
+        } else {   // one GPU only (refused at creation otherwise)
             if ((e = launch_swiglu_on_stream(d->gate, d->up, d->gate, F, s))) return fail(d, e, "swiglu");
-            if ((e = mg_matvec_kquant_on_stream(L.type[6], L.wdown, d->gate, 0, d->hidden, d->hidden, D, F / 256, s)))
-                return fail(d, e, "down");
-            d->mixed_launches += 2;
+            d->mixed_launches += 1;
+            if ((e = project_add(d, L.type[6], L.wdown, d->gate, 0, d->tmp_down, kSiteDown, F, "down"))) return e;
         }
     }
     if ((e = launch_rms_norm_on_stream(d->hidden, d->out_norm, d->cur, 1, D, c.rms_eps, s))) return fail(d, e, "rms_norm");
-    if ((e = typed_matvec(d, d->head_type, d->lm_head, d->cur, d->logits, c.vocab, D))) return fail(d, e, "lm_head");
-    if ((e = mg_argmax_on_stream(d->logits, c.vocab, tok_dev, d->argmax_scratch, d->history, step_dev, s))) return fail(d, e, "argmax");
+    if ((e = typed_matvec(d, d->head_type, d->lm_head, d->cur, d->logits, d->v_loc, D))) return fail(d, e, "lm_head");
+    if (!sharded) {
+        if ((e = mg_argmax_on_stream(d->logits, c.vocab, tok_dev, d->argmax_scratch, d->history, step_dev, s)))
+            return fail(d, e, "argmax");
+    } else {
+        // local best -> (value, global index) pairs of all ranks -> the same global choice everywhere
+        int* local_tok = reinterpret_cast<int*>(static_cast<char*>(d->argmax_scratch) + 2048);
+        if ((e = mg_argmax_on_stream(d->logits, d->v_loc, local_tok, d->argmax_scratch, nullptr, nullptr, s)))
+            return fail(d, e, "argmax");
+        mg::launch_pdl(local_pair_kernel, dim3(1), dim3(1), 0, d->stream, (const float*)d->logits, (const int*)local_tok,
+                       d->rank * d->v_loc, d->pair_buf + 2 * d->rank, mgpeer::PeerSync{});
+        if ((e = gather_equal(d, kSitePairs, d->pair_buf, 2, mgnccl::kFloat32, 4))) return e;
+        mg::launch_pdl(argmax_pairs_kernel, dim3(1), dim3(1), 0, d->stream, (const float*)d->pair_buf, d->world, tok_dev, d->history,
+                       (const int*)step_dev);
+        d->mixed_launches += 2;
+    }
     mg::launch_pdl(advance_state_kernel, dim3(1), dim3(1), 0, d->stream, d->state);
     d->mixed_launches += 5;
     if ((e = (int)cudaGetLastError())) return fail(d, e, "advance");
@@ -711,6 +744,8 @@ int create_impl(const mg_decoder_config* cfg, int rank, int world, const void* n
                 d->layers[l].type[i] = (uint8_t)proj_types[l * 7 + i];
                 d->mixed = d->mixed || proj_types[l * 7 + i] != kTypeQ4K;
             }
+    // a sharded typed engine exchanges the SwiGLU output as limb records, which one CTA must be able to hold
+    if (d->mixed && world > 1 && (size_t)(c.d_ff / 256) * 4 * 208 > (size_t)200 * 1024) return bail((int)cudaErrorInvalidValue);
     {   // Every weight lives in ONE device allocation addressed by offset, as the reference's engine
         // packs its quantised tensors (crates/modgrad-gemma/src/rocm_gemma.rs:206-224); 256-byte
         // aligned sub-ranges, so every Q4_K row stays 16-byte aligned.
@@ -806,6 +841,7 @@ int create_impl(const mg_decoder_config* cfg, int rank, int world, const void* n
     int init[4] = {0, 1, 0, 0};
     if ((e = cudaMemcpy(d->state, init, sizeof init, cudaMemcpyHostToDevice)) != cudaSuccess) return bail((int)e);
     if (world > 1 && (rc = setup_peer_exchange(d))) return bail(rc);
+    if (d->mixed) d->fused = d->stamped = false;  // the typed path gathers with separate kernels (or NCCL)
     *out = d;
     return 0;
 }
@@ -819,20 +855,25 @@ int mg_decoder_create_sharded(const mg_decoder_config* cfg, int rank, int world,
     return create_impl(cfg, rank, world, nccl_id128, nullptr, kTypeF16, kTypeF16, out);
 }
 
-// A single-GPU engine whose tensors carry their own GGUF types, as real checkpoints mix them
+// An engine whose tensors carry their own GGUF types, as real checkpoints mix them
 // (crates/modgrad-gemma/src/rocm_gemma.rs:291-309 dispatches per tensor the same way): every projection
 // Q4_K (12), Q5_K (13) or Q6_K (14); the token embedding and the LM head F16 (1) or one of the three.
 // proj_types holds n_layers * 7 ids in the order q, k, v, o, gate, up, down.  An engine whose types are
-// all the defaults is the one mg_decoder_create builds.
-int mg_decoder_create_typed(const mg_decoder_config* cfg, const int* proj_types, int embed_type, int head_type,
-                            mg_decoder** out) {
+// all the defaults is the one mg_decoder_create_sharded builds.  Row-sharded like that one (same row
+// ranges, same uploads), with the exchanges as separate gathers.
+int mg_decoder_create_typed_sharded(const mg_decoder_config* cfg, const int* proj_types, int embed_type, int head_type,
+                                    int rank, int world, const void* nccl_id128, mg_decoder** out) {
     if (!cfg || !proj_types || !out) return (int)cudaErrorInvalidValue;
     auto quant = [](int t) { return t == kTypeQ4K || t == kTypeQ5K || t == kTypeQ6K; };
     for (int i = 0; i < cfg->n_layers * 7; ++i)
         if (!quant(proj_types[i])) return (int)cudaErrorInvalidValue;
     if ((embed_type != kTypeF16 && !quant(embed_type)) || (head_type != kTypeF16 && !quant(head_type)))
         return (int)cudaErrorInvalidValue;
-    return create_impl(cfg, 0, 1, nullptr, proj_types, embed_type, head_type, out);
+    return create_impl(cfg, rank, world, nccl_id128, proj_types, embed_type, head_type, out);
+}
+int mg_decoder_create_typed(const mg_decoder_config* cfg, const int* proj_types, int embed_type, int head_type,
+                            mg_decoder** out) {
+    return mg_decoder_create_typed_sharded(cfg, proj_types, embed_type, head_type, 0, 1, nullptr, out);
 }
 
 int mg_decoder_create(const mg_decoder_config* cfg, mg_decoder** out) {

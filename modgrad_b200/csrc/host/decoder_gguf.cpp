@@ -6,7 +6,7 @@
 // for the engine in decoder.cpp: Q4_K / Q5_K / Q6_K projections, f32 norm weights, token embedding and
 // LM head in half or one of the three K-quants (the head tied to the embedding when the file has no
 // output.weight, llm.rs:1281-1286).  A file whose projections are all Q4_K with half embedding and
-// head gets the default engine (which also row-shards); any other mix gets the typed engine, one GPU.  Tensor bytes go
+// head gets the default engine; any other mix gets the typed engine (both row-shard the same way).  Tensor bytes go
 // from the memory-mapped file straight to the device, never re-encoded; a row-sharded rank
 // uploads only its row ranges (rows are contiguous byte ranges of the row-major block array).
 #include <cuda_runtime.h>
@@ -171,9 +171,6 @@ int mg_decoder_load_gguf(const char* path, int max_seq, int rank, int world, con
     if ((rc = add_rows(head, 0, MG_W_LM_HEAD, kQuantOrHalf, D, c.vocab, (size_t)rank * v_loc, v_loc))) return rc;
     if ((rc = add_rows("output_norm.weight", 0, MG_W_OUT_NORM, kF32Only, D, 1, 0, 1))) return rc;
 
-    if (!all_default && world != 1)
-        return fail(-4, "row sharding needs Q4_K projections with a half embedding and LM head; this file mixes other tensor types");
-
     // VRAM guard (rocm_gemma.rs:110-138): weights + KV cache + activations must fit with headroom.
     resident += (size_t)c.n_layers * 2 * (size_t)max_seq * (kv1 - kv0) * hd * 2;  // half K and V
     resident += (size_t)(4 * D + 2 * f_loc + q_dim + v_loc) * 4 + (size_t)F * 4 + (8u << 20);
@@ -191,7 +188,7 @@ int mg_decoder_load_gguf(const char* path, int max_seq, int rank, int world, con
 
     mg_decoder* d = nullptr;
     rc = all_default ? mg_decoder_create_sharded(&c, rank, world, nccl_id128, &d)
-                     : mg_decoder_create_typed(&c, proj_types.data(), embed_type, head_type, &d);
+                     : mg_decoder_create_typed_sharded(&c, proj_types.data(), embed_type, head_type, rank, world, nccl_id128, &d);
     if (rc) return fail(rc, std::string("mg_decoder_create: ") + cudaGetErrorString((cudaError_t)rc));
     for (const Piece& pc : pieces) {
         rc = mg_decoder_upload(d, pc.layer, pc.which, pc.src, pc.bytes);

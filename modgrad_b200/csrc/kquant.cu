@@ -184,8 +184,8 @@ __device__ __forceinline__ float4 ld_x4(const float* p, bool aligned) {
 template <int KIND, int R, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) matvec_kquant_kernel(const uint8_t* __restrict__ w, const float* x,
                                                                    const float* add, float* y, int out_dim, int bpr,
-                                                                   int x_aligned) {
-    mg::pdl_prologue();
+                                                                   int x_aligned, int hold_trigger) {
+    mg::pdl_prologue(hold_trigger);
     __shared__ float part[WARPS][R];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int kBytes = KIND == 5 ? kQ5Bytes : kQ6Bytes;
@@ -448,10 +448,10 @@ constexpr int kLimbThreads = 256, kLimbWarps = kLimbThreads / 32;
 // y[row] = (add ? add[row] : 0) + W[row] . x.
 template <class FMT, int R, int FROM_X>
 __device__ __forceinline__ void limbs_short_body(const uint8_t* __restrict__ w, const void* src, const float* add, float* y,
-                                                 int out_dim, int bpr, int x_aligned) {
+                                                 int out_dim, int bpr, int x_aligned, int hold_trigger) {
     extern __shared__ __align__(16) uint4 rec_s[];
     const uint32_t* rec_w = reinterpret_cast<const uint32_t*>(rec_s);
-    mg::pdl_prologue();
+    mg::pdl_prologue(hold_trigger);
     limbs_stage_records<FROM_X, kLimbThreads>(src, bpr, x_aligned, rec_s);
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -481,14 +481,14 @@ __device__ __forceinline__ void limbs_short_body(const uint8_t* __restrict__ w, 
 template <int R, int FROM_X>
 __global__ void __launch_bounds__(kLimbThreads, 4) matvec_q6k_limbs_kernel(const uint8_t* __restrict__ w, const void* src,
                                                                            const float* add, float* y, int out_dim, int bpr,
-                                                                           int x_aligned) {
-    limbs_short_body<Q6Fmt, R, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned);
+                                                                           int x_aligned, int hold_trigger) {
+    limbs_short_body<Q6Fmt, R, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned, hold_trigger);
 }
 template <int R, int FROM_X>
 __global__ void __launch_bounds__(kLimbThreads, 3) matvec_q5k_limbs_kernel(const uint8_t* __restrict__ w, const void* src,
                                                                            const float* add, float* y, int out_dim, int bpr,
-                                                                           int x_aligned) {
-    limbs_short_body<Q5Fmt, R, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned);
+                                                                           int x_aligned, int hold_trigger) {
+    limbs_short_body<Q5Fmt, R, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned, hold_trigger);
 }
 
 // Long rows, few of them (a down projection): one CTA per SM keeps the records (one copy per SM, not
@@ -499,7 +499,7 @@ constexpr int kLongThreads = 768, kLongGroups = kLongThreads / 8, kLongRows = 32
 
 template <class FMT, int FROM_X>
 __device__ __forceinline__ void limbs_long_body(const uint8_t* __restrict__ w, const void* src, const float* add, float* y,
-                                                int out_dim, int bpr, int x_aligned) {
+                                                int out_dim, int bpr, int x_aligned, int hold_trigger) {
     extern __shared__ __align__(16) uint4 rec_s[];
     const uint32_t* rec_w = reinterpret_cast<const uint32_t*>(rec_s);
     float* part = reinterpret_cast<float*>(rec_s + (size_t)bpr * 4 * xlimbs::kRecordVec4);   // [kLongRows][kLongGroups]
@@ -515,7 +515,7 @@ __device__ __forceinline__ void limbs_long_body(const uint8_t* __restrict__ w, c
     typename FMT::Lane nxt[1];
     if (group < min(kLongRows, row_end - row_begin) * bpr)
         FMT::load(nxt[0], w + (size_t)row_begin * row_bytes + (size_t)group * FMT::kBytes, sub);
-    mg::pdl_prologue();
+    mg::pdl_prologue(hold_trigger);
     limbs_stage_records<FROM_X, kLongThreads>(src, bpr, x_aligned, rec_s);
 
     for (int pass0 = row_begin; pass0 < row_end; pass0 += kLongRows) {
@@ -568,14 +568,14 @@ __device__ __forceinline__ void limbs_long_body(const uint8_t* __restrict__ w, c
 template <int FROM_X>
 __global__ void __launch_bounds__(kLongThreads, 1) matvec_q6k_limbs_long_kernel(const uint8_t* __restrict__ w, const void* src,
                                                                                 const float* add, float* y, int out_dim,
-                                                                                int bpr, int x_aligned) {
-    limbs_long_body<Q6Fmt, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned);
+                                                                                int bpr, int x_aligned, int hold_trigger) {
+    limbs_long_body<Q6Fmt, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned, hold_trigger);
 }
 template <int FROM_X>
 __global__ void __launch_bounds__(kLongThreads, 1) matvec_q5k_limbs_long_kernel(const uint8_t* __restrict__ w, const void* src,
                                                                                 const float* add, float* y, int out_dim,
-                                                                                int bpr, int x_aligned) {
-    limbs_long_body<Q5Fmt, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned);
+                                                                                int bpr, int x_aligned, int hold_trigger) {
+    limbs_long_body<Q5Fmt, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned, hold_trigger);
 }
 
 // Q6_K weights x int8 activations (xq / xd / xsum from launch_quantize_q8_1):
@@ -625,7 +625,8 @@ int launch_matvec_shape(const uint8_t* w, const float* x, const float* add, floa
     const int resident = sms * (2048 / (WARPS * 32));
     if (grid > resident) grid = resident;
     return (int)mg::launch_pdl(matvec_kquant_kernel<KIND, R, WARPS>, dim3((unsigned)grid), dim3(WARPS * 32), 0,
-                               (cudaStream_t)stream, w, x, add, y, out_dim, bpr, mg::aligned16(x) ? 1 : 0);
+                               (cudaStream_t)stream, w, x, add, y, out_dim, bpr, mg::aligned16(x) ? 1 : 0,
+                               mg::early_trigger_flag() ? 0 : 1);
 }
 
 template <int KIND>
@@ -662,8 +663,9 @@ int launch_limbs_kernel(Kernel kernel, size_t& configured, unsigned grid, int th
         if (e != cudaSuccess) return (int)e;
         configured = (size_t)dp.max_smem_optin;
     }
+    // a collective of another library may follow and start on the early trigger: the host switches it off then
     return (int)mg::launch_pdl(kernel, dim3(grid), dim3((unsigned)threads), smem, (cudaStream_t)stream, w, src, add, y, out_dim,
-                               bpr, mg::aligned16(src) ? 1 : 0);
+                               bpr, mg::aligned16(src) ? 1 : 0, mg::early_trigger_flag() ? 0 : 1);
 }
 
 template <int KIND, int FROM_X>

@@ -108,7 +108,7 @@ class Q4KDecoder:
 
     def __init__(self, cfg: DecoderConfig, rank: int = 0, world: int = 1, nccl_id: bytes | None = None,
                  types: tuple | None = None):
-        """``types`` = (proj_types, embed_type, head_type) builds the typed single-GPU engine: proj_types
+        """``types`` = (proj_types, embed_type, head_type) builds the typed engine: proj_types
         holds, per layer, the GGUF type ids (12 Q4_K, 13 Q5_K, 14 Q6_K) of q, k, v, o, gate, up, down;
         embed_type / head_type are 1 (F16) or one of the three."""
         self.cfg = cfg
@@ -118,11 +118,10 @@ class Q4KDecoder:
         cs = cfg.c_struct()
         idbuf = C.create_string_buffer(nccl_id, 128) if nccl_id is not None else None
         if types is not None:
-            if world != 1:
-                raise Runtime("the typed engine runs on one GPU")
             proj, embed_type, head_type = types
             flat = np.ascontiguousarray(np.asarray(proj, dtype=np.int32).reshape(cfg.n_layers * 7))
-            code = self._lib.mg_decoder_create_typed(C.byref(cs), _p(flat), int(embed_type), int(head_type), C.byref(h))
+            code = self._lib.mg_decoder_create_typed_sharded(C.byref(cs), _p(flat), int(embed_type), int(head_type), rank,
+                                                             world, idbuf, C.byref(h))
         else:
             code = self._lib.mg_decoder_create_sharded(C.byref(cs), rank, world, idbuf, C.byref(h))
         if code != 0 or not h.value:

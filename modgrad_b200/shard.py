@@ -53,9 +53,8 @@ def decoder_shard(cfg, rank: int, world: int) -> DecoderShard:
 
 
 def q4k_rows(w: np.ndarray, out_dim: int, in_dim: int, lo: int, hi: int) -> np.ndarray:
-    """Rows [lo, hi) of a row-major Q4_K matrix, as bytes."""
-    row_bytes = (in_dim // 256) * 144
-    return np.ascontiguousarray(w.reshape(out_dim, row_bytes)[lo:hi]).reshape(-1)
+    """Rows [lo, hi) of a row-major block-quantised matrix (Q4_K, Q5_K, Q6_K: whole rows of blocks), as bytes."""
+    return np.ascontiguousarray(w.reshape(out_dim, w.size // out_dim)[lo:hi]).reshape(-1)
 
 
 def slice_layer(cfg, sh: DecoderShard, lw: dict) -> dict:

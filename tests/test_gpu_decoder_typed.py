@@ -214,6 +214,3 @@ def test_mixed_gguf_loads_into_the_typed_engine(orc, tmp_path, tied):
             assert base <= a.weight_ptr(l, which) < base + nbytes and a.weight_ptr(l, which) % 256 == 0
     a.close()
     b.close()
-    # a mixed file cannot be row-sharded
-    with pytest.raises(Runtime, match="row sharding needs"):
-        dec.Q4KDecoder.from_gguf(path, cfg.max_seq, rank=0, world=2, nccl_id=b"\0" * 128)

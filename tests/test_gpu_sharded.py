@@ -33,6 +33,21 @@ def test_sharded_decoder_matches_oracle(cuda, world, mode):
     assert "SHARDED_OK" in r.stdout and "PEER_MATVEC_OK" in r.stdout, r.stdout[-1500:]
 
 
+@pytest.mark.parametrize("world,mode", [(2, "stamped"), (2, "nccl"), (4, "stamped")])
+def test_sharded_typed_engine_from_a_mixed_gguf_matches_oracle(cuda, world, mode):
+    """Q4_K / Q5_K / Q6_K projections with a Q6_K embedding and LM head, row-sharded: the typed engine gathers
+    with peer-store kernels whatever fused mode is asked for, or with NCCL."""
+    if gpu_count(cuda) < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MODGRAD_DECODER_GATHER=mode)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(29700 + world),
+                        str(ROOT / "tests" / "typed_sharded_worker.py")],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
+    assert "TYPED_SHARDED_OK" in r.stdout, r.stdout[-1500:]
+
+
 @pytest.mark.parametrize("mode", ["stamped", "fused"])
 def test_bounded_wait_runs_out_when_a_peer_does_not_launch(cuda, mode):
     """A peer that skips a step between launches: the waiting rank's bounded wait expires, the token
