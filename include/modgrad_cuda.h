@@ -106,6 +106,12 @@ int launch_matvec_q6k_on_stream(const uint8_t* w_q6, const float* x, float* y, i
  * the kernel launched immediately before on the same stream. */
 int mg_matvec_kquant_on_stream(int ggml_type, const uint8_t* w, const void* x, int x_kind, const float* add, float* y,
                                int out_dim, int blocks_per_row, void* stream);
+/* y = W . rms_norm(x) for a Q5_K (13) or Q6_K (14) weight: the RMSNorm of the decode loop
+ * (crates/modgrad-device/src/kfd/llm.rs:921-928, Plain) done by every CTA while it converts x, like
+ * mg_rmsnorm_matvec_q4k_multi_on_stream for Q4_K.  Integer kernels only: cudaErrorInvalidValue when the weight
+ * is not 4-byte aligned or a row's records exceed one CTA's shared memory. */
+int mg_rmsnorm_matvec_kquant_on_stream(int ggml_type, const uint8_t* w, const float* x, const float* norm_w, float eps,
+                                       float* y, int out_dim, int blocks_per_row, void* stream);
 int launch_matvec_q6k_dp4a(const uint8_t* w, const int8_t* xq, const float* xd, const float* xsum, float* y,
                            int out_dim, int bpr);
 int launch_matvec_q6k_dp4a_on_stream(const uint8_t* w, const int8_t* xq, const float* xd, const float* xsum,

@@ -100,6 +100,7 @@ SIGNATURES = {
     "mg_decoder_create_typed_sharded": (ci, [vp, vp, ci, ci, ci, ci, vp, C.POINTER(vp)]),
     "mg_decoder_weight_type": (ci, [vp, ci, ci]),
     "mg_matvec_kquant_on_stream": (ci, [ci, vp, vp, ci, vp, vp, ci, ci, vp]),
+    "mg_rmsnorm_matvec_kquant_on_stream": (ci, [ci, vp, vp, vp, C.c_float, vp, ci, ci, vp]),
     "mg_embed_kquant_on_stream": (ci, [vp, ci, ci, vp, vp, ci, ci, vp]),
     "mg_nccl_unique_id": (ci, [vp]),
     "mg_decoder_shard_ranges": (ci, [vp, ci, ci, vp]),

@@ -423,8 +423,9 @@ int typed_matvec(mg_decoder* d, int type, const void* w, const float* x, float* 
 }
 
 // y[i] = W[i] . rms_norm(hidden) for n tensors of one input.  All Q4_K: the one fused launch of the
-// default path.  Otherwise the normalised vector is written once, the Q4_K tensors share one launch
-// and every other tensor takes the launcher of its type.
+// default path.  Otherwise the Q4_K tensors share one launch and every other tensor takes the launcher
+// of its type, each with the RMSNorm fused in front; only for rows too long for that is the normalised
+// vector written once by a launch of its own.
 int norm_project(mg_decoder* d, int n, const uint8_t* const* w, const uint8_t* types, const float* norm_w, float* const* y,
                  const int* rows, int cols, const char* what) {
     int e, n4 = 0;
@@ -437,6 +438,23 @@ int norm_project(mg_decoder* d, int n, const uint8_t* const* w, const uint8_t* t
         e = mg_rmsnorm_matvec_q4k_multi_on_stream(n, w, d->hidden, norm_w, d->cfg.rms_eps, nullptr, y, rows, cols / 256, d->stream);
         d->mixed_launches += 1;
         return e ? fail(d, e, what) : 0;
+    }
+    if ((size_t)(cols / 256) * 4 * 208 <= (size_t)200 * 1024) {
+        // every launch normalises for itself while it converts the activations: no separate RMSNorm launch
+        if (n4) {
+            if ((e = mg_rmsnorm_matvec_q4k_multi_on_stream(n4, w4, d->hidden, norm_w, d->cfg.rms_eps, nullptr, y4, rows4, cols / 256,
+                                                           d->stream)))
+                return fail(d, e, what);
+            d->mixed_launches += 1;
+        }
+        for (int i = 0; i < n; ++i) {
+            if (types[i] == kTypeQ4K) continue;
+            if ((e = mg_rmsnorm_matvec_kquant_on_stream(types[i], w[i], d->hidden, norm_w, d->cfg.rms_eps, y[i], rows[i], cols / 256,
+                                                        d->stream)))
+                return fail(d, e, what);
+            d->mixed_launches += 1;
+        }
+        return 0;
     }
     if ((e = launch_rms_norm_on_stream(d->hidden, norm_w, d->cur, 1, cols, d->cfg.rms_eps, d->stream))) return fail(d, e, "rms_norm");
     d->mixed_launches += 1;
@@ -541,8 +559,17 @@ int queue_token_mixed(mg_decoder* d) {
             if ((e = project_add(d, L.type[6], L.wdown, d->gate, 0, d->tmp_down, kSiteDown, F, "down"))) return e;
         }
     }
-    if ((e = launch_rms_norm_on_stream(d->hidden, d->out_norm, d->cur, 1, D, c.rms_eps, s))) return fail(d, e, "rms_norm");
-    if ((e = typed_matvec(d, d->head_type, d->lm_head, d->cur, d->logits, d->v_loc, D))) return fail(d, e, "lm_head");
+    if (d->head_type != kTypeF16 && (size_t)(D / 256) * 4 * 208 <= (size_t)200 * 1024) {   // final RMSNorm inside the head's launch
+        const uint8_t* w[1] = {reinterpret_cast<const uint8_t*>(d->lm_head)};
+        float* y[1] = {d->logits};
+        const int rows[1] = {d->v_loc};
+        const uint8_t t[1] = {(uint8_t)d->head_type};
+        if ((e = norm_project(d, 1, w, t, d->out_norm, y, rows, D, "lm_head"))) return e;
+        d->mixed_launches -= 2;   // counted with the tail below
+    } else {
+        if ((e = launch_rms_norm_on_stream(d->hidden, d->out_norm, d->cur, 1, D, c.rms_eps, s))) return fail(d, e, "rms_norm");
+        if ((e = typed_matvec(d, d->head_type, d->lm_head, d->cur, d->logits, d->v_loc, D))) return fail(d, e, "lm_head");
+    }
     if (!sharded) {
         if ((e = mg_argmax_on_stream(d->logits, c.vocab, tok_dev, d->argmax_scratch, d->history, step_dev, s)))
             return fail(d, e, "argmax");

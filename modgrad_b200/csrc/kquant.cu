@@ -422,15 +422,47 @@ struct Q5Fmt {
 };
 
 // The activation vector as limb records in shared memory.  FROM_X = 1: src is the f32 vector, converted
-// here; 0: src holds records (mg_q4k_x_to_limbs_on_stream, mg_swiglu_limbs_on_stream).
+// here; 0: src holds records (mg_q4k_x_to_limbs_on_stream, mg_swiglu_limbs_on_stream).  With norm_w
+// (FROM_X only) the vector is RMS-normalised first (crates/modgrad-device/src/kfd/llm.rs:921-928, Plain):
+// x * (1 / sqrt(mean(x^2) + eps)) * w, the sum of squares in one pass, the scaling in a second one that
+// reads x again (it is in L2) instead of keeping it in registers.
 template <int FROM_X, int THREADS>
-__device__ __forceinline__ void limbs_stage_records(const void* src, int bpr, int x_aligned, uint4* rec_s) {
+__device__ __forceinline__ void limbs_stage_records(const void* src, int bpr, int x_aligned, uint4* rec_s,
+                                                    const float* norm_w = nullptr, float eps = 0.0f) {
     if (FROM_X) {
         const float* x = static_cast<const float*>(src);
         const int n_chunks = bpr * 64;   // a multiple of 64: warps are whole
+        float inv = 1.0f;
+        const bool w_aligned = (reinterpret_cast<uintptr_t>(norm_w) & 15u) == 0;
+        if (norm_w != nullptr) {
+            __shared__ float red[THREADS / 32 + 1];
+            float p = 0.0f;
+            for (int c = threadIdx.x; c < n_chunks; c += THREADS) {
+                float v[4];
+                gemvdev::load_chunk<false>(v, x, c, x_aligned);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) p = fmaf(v[i], v[i], p);
+            }
+            p = q4k::warp_sum(p);
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = p;
+            __syncthreads();
+            if (threadIdx.x < 32) {
+                float t = threadIdx.x < THREADS / 32 ? red[threadIdx.x] : 0.0f;
+                t = q4k::warp_sum(t);
+                if (threadIdx.x == 0) red[THREADS / 32] = t;
+            }
+            __syncthreads();
+            inv = 1.0f / sqrtf(red[THREADS / 32] / (float)(bpr * 256) + eps);
+        }
         for (int c = threadIdx.x; c < n_chunks; c += THREADS) {
             float v[4];
             gemvdev::load_chunk<false>(v, x, c, x_aligned);
+            if (norm_w != nullptr) {
+                float wv[4];
+                gemvdev::load_chunk<false>(wv, norm_w, c, w_aligned ? 1 : 0);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[i] = v[i] * inv * wv[i];
+            }
             gemvdev::convert_chunk(v, c, reinterpret_cast<uint32_t*>(rec_s));
         }
     } else {
@@ -448,11 +480,12 @@ constexpr int kLimbThreads = 256, kLimbWarps = kLimbThreads / 32;
 // y[row] = (add ? add[row] : 0) + W[row] . x.
 template <class FMT, int R, int FROM_X>
 __device__ __forceinline__ void limbs_short_body(const uint8_t* __restrict__ w, const void* src, const float* add, float* y,
-                                                 int out_dim, int bpr, int x_aligned, int hold_trigger) {
+                                                 int out_dim, int bpr, int x_aligned, int hold_trigger, const float* norm_w,
+                                                 float eps) {
     extern __shared__ __align__(16) uint4 rec_s[];
     const uint32_t* rec_w = reinterpret_cast<const uint32_t*>(rec_s);
     mg::pdl_prologue(hold_trigger);
-    limbs_stage_records<FROM_X, kLimbThreads>(src, bpr, x_aligned, rec_s);
+    limbs_stage_records<FROM_X, kLimbThreads>(src, bpr, x_aligned, rec_s, norm_w, eps);
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int bsel = lane >> 3, sub = lane & 7;
@@ -481,14 +514,16 @@ __device__ __forceinline__ void limbs_short_body(const uint8_t* __restrict__ w, 
 template <int R, int FROM_X>
 __global__ void __launch_bounds__(kLimbThreads, 4) matvec_q6k_limbs_kernel(const uint8_t* __restrict__ w, const void* src,
                                                                            const float* add, float* y, int out_dim, int bpr,
-                                                                           int x_aligned, int hold_trigger) {
-    limbs_short_body<Q6Fmt, R, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned, hold_trigger);
+                                                                           int x_aligned, int hold_trigger, const float* norm_w,
+                                                                           float eps) {
+    limbs_short_body<Q6Fmt, R, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned, hold_trigger, norm_w, eps);
 }
 template <int R, int FROM_X>
 __global__ void __launch_bounds__(kLimbThreads, 3) matvec_q5k_limbs_kernel(const uint8_t* __restrict__ w, const void* src,
                                                                            const float* add, float* y, int out_dim, int bpr,
-                                                                           int x_aligned, int hold_trigger) {
-    limbs_short_body<Q5Fmt, R, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned, hold_trigger);
+                                                                           int x_aligned, int hold_trigger, const float* norm_w,
+                                                                           float eps) {
+    limbs_short_body<Q5Fmt, R, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned, hold_trigger, norm_w, eps);
 }
 
 // Long rows, few of them (a down projection): one CTA per SM keeps the records (one copy per SM, not
@@ -499,7 +534,8 @@ constexpr int kLongThreads = 768, kLongGroups = kLongThreads / 8, kLongRows = 32
 
 template <class FMT, int FROM_X>
 __device__ __forceinline__ void limbs_long_body(const uint8_t* __restrict__ w, const void* src, const float* add, float* y,
-                                                int out_dim, int bpr, int x_aligned, int hold_trigger) {
+                                                int out_dim, int bpr, int x_aligned, int hold_trigger, const float* norm_w,
+                                                float eps) {
     extern __shared__ __align__(16) uint4 rec_s[];
     const uint32_t* rec_w = reinterpret_cast<const uint32_t*>(rec_s);
     float* part = reinterpret_cast<float*>(rec_s + (size_t)bpr * 4 * xlimbs::kRecordVec4);   // [kLongRows][kLongGroups]
@@ -516,7 +552,7 @@ __device__ __forceinline__ void limbs_long_body(const uint8_t* __restrict__ w, c
     if (group < min(kLongRows, row_end - row_begin) * bpr)
         FMT::load(nxt[0], w + (size_t)row_begin * row_bytes + (size_t)group * FMT::kBytes, sub);
     mg::pdl_prologue(hold_trigger);
-    limbs_stage_records<FROM_X, kLongThreads>(src, bpr, x_aligned, rec_s);
+    limbs_stage_records<FROM_X, kLongThreads>(src, bpr, x_aligned, rec_s, norm_w, eps);
 
     for (int pass0 = row_begin; pass0 < row_end; pass0 += kLongRows) {
         const int n_rows = min(kLongRows, row_end - pass0);
@@ -568,14 +604,16 @@ __device__ __forceinline__ void limbs_long_body(const uint8_t* __restrict__ w, c
 template <int FROM_X>
 __global__ void __launch_bounds__(kLongThreads, 1) matvec_q6k_limbs_long_kernel(const uint8_t* __restrict__ w, const void* src,
                                                                                 const float* add, float* y, int out_dim,
-                                                                                int bpr, int x_aligned, int hold_trigger) {
-    limbs_long_body<Q6Fmt, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned, hold_trigger);
+                                                                                int bpr, int x_aligned, int hold_trigger,
+                                                                                const float* norm_w, float eps) {
+    limbs_long_body<Q6Fmt, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned, hold_trigger, norm_w, eps);
 }
 template <int FROM_X>
 __global__ void __launch_bounds__(kLongThreads, 1) matvec_q5k_limbs_long_kernel(const uint8_t* __restrict__ w, const void* src,
                                                                                 const float* add, float* y, int out_dim,
-                                                                                int bpr, int x_aligned, int hold_trigger) {
-    limbs_long_body<Q5Fmt, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned, hold_trigger);
+                                                                                int bpr, int x_aligned, int hold_trigger,
+                                                                                const float* norm_w, float eps) {
+    limbs_long_body<Q5Fmt, FROM_X>(w, src, add, y, out_dim, bpr, x_aligned, hold_trigger, norm_w, eps);
 }
 
 // Q6_K weights x int8 activations (xq / xd / xsum from launch_quantize_q8_1):
@@ -651,25 +689,32 @@ size_t limbs_smem_bytes(int out_dim, int bpr) {
 }
 bool limbs_ok(const uint8_t* w, int out_dim, int bpr) {
     const mg::DeviceProps& dp = mg::device_props();
-    return (reinterpret_cast<uintptr_t>(w) & 3u) == 0 && dp.ok && limbs_smem_bytes(out_dim, bpr) <= (size_t)dp.max_smem_optin;
+    // 256 bytes left for the kernels' static shared memory (the RMSNorm reduction)
+    return (reinterpret_cast<uintptr_t>(w) & 3u) == 0 && dp.ok && limbs_smem_bytes(out_dim, bpr) + 256 <= (size_t)dp.max_smem_optin;
 }
 
 template <class Kernel>
 int launch_limbs_kernel(Kernel kernel, size_t& configured, unsigned grid, int threads, size_t smem, const uint8_t* w,
-                        const void* src, const float* add, float* y, int out_dim, int bpr, void* stream) {
+                        const void* src, const float* add, float* y, int out_dim, int bpr, void* stream, const float* norm_w,
+                        float eps) {
     if (smem > 48 * 1024 && smem > configured) {   // configured: the largest dynamic shared memory set for this kernel
         const mg::DeviceProps& dp = mg::device_props();
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.max_smem_optin);
+        cudaFuncAttributes fa;
+        cudaError_t e = cudaFuncGetAttributes(&fa, kernel);
         if (e != cudaSuccess) return (int)e;
-        configured = (size_t)dp.max_smem_optin;
+        const int most = dp.max_smem_optin - (int)fa.sharedSizeBytes;   // the kernel's static shared memory counts too
+        if ((size_t)most < smem) return (int)cudaErrorInvalidValue;
+        if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most)) != cudaSuccess) return (int)e;
+        configured = (size_t)most;
     }
     // a collective of another library may follow and start on the early trigger: the host switches it off then
     return (int)mg::launch_pdl(kernel, dim3(grid), dim3((unsigned)threads), smem, (cudaStream_t)stream, w, src, add, y, out_dim,
-                               bpr, mg::aligned16(src) ? 1 : 0, mg::early_trigger_flag() ? 0 : 1);
+                               bpr, mg::aligned16(src) ? 1 : 0, mg::early_trigger_flag() ? 0 : 1, norm_w, eps);
 }
 
 template <int KIND, int FROM_X>
-int launch_limbs(const uint8_t* w, const void* src, const float* add, float* y, int out_dim, int bpr, void* stream) {
+int launch_limbs(const uint8_t* w, const void* src, const float* add, float* y, int out_dim, int bpr, void* stream,
+                 const float* norm_w = nullptr, float eps = 0.0f) {
     const mg::DeviceProps& dp = mg::device_props();
     const size_t smem = limbs_smem_bytes(out_dim, bpr);
     if (limbs_long_shape(out_dim, bpr)) {
@@ -677,9 +722,9 @@ int launch_limbs(const uint8_t* w, const void* src, const float* add, float* y, 
         const unsigned grid = (unsigned)(out_dim < dp.sm_count ? out_dim : dp.sm_count);
         if (KIND == 5)
             return launch_limbs_kernel(matvec_q5k_limbs_long_kernel<FROM_X>, configured, grid, kLongThreads, smem, w, src, add, y,
-                                       out_dim, bpr, stream);
+                                       out_dim, bpr, stream, norm_w, eps);
         return launch_limbs_kernel(matvec_q6k_limbs_long_kernel<FROM_X>, configured, grid, kLongThreads, smem, w, src, add, y,
-                                   out_dim, bpr, stream);
+                                   out_dim, bpr, stream, norm_w, eps);
     }
     constexpr int R = 2;
     static size_t configured = 0;
@@ -690,9 +735,9 @@ int launch_limbs(const uint8_t* w, const void* src, const float* add, float* y, 
     if (grid > dp.sm_count * per_sm) grid = dp.sm_count * per_sm;
     if (KIND == 5)
         return launch_limbs_kernel(matvec_q5k_limbs_kernel<R, FROM_X>, configured, (unsigned)grid, kLimbThreads, smem, w, src, add,
-                                   y, out_dim, bpr, stream);
+                                   y, out_dim, bpr, stream, norm_w, eps);
     return launch_limbs_kernel(matvec_q6k_limbs_kernel<R, FROM_X>, configured, (unsigned)grid, kLimbThreads, smem, w, src, add, y,
-                               out_dim, bpr, stream);
+                               out_dim, bpr, stream, norm_w, eps);
 }
 
 // x_kind 0: f32 activations; 1: limb records.
@@ -749,6 +794,20 @@ int launch_matvec_q6k_dp4a_on_stream(const uint8_t* w, const int8_t* xq, const f
 int launch_matvec_q6k_dp4a(const uint8_t* w, const int8_t* xq, const float* xd, const float* xsum, float* y, int out_dim,
                            int bpr) {
     return launch_matvec_q6k_dp4a_on_stream(w, xq, xd, xsum, y, out_dim, bpr, nullptr);
+}
+
+// y = W . rms_norm(x) for a Q5_K (ggml_type 13) or Q6_K (14) weight: the RMSNorm the decode loop runs in front
+// of a projection (crates/modgrad-device/src/kfd/llm.rs:921-928, Plain) done by every CTA while it converts x,
+// like mg_rmsnorm_matvec_q4k_multi_on_stream for Q4_K.  Runs on the limb kernels only: cudaErrorInvalidValue
+// when the weight is not 4-byte aligned or the records of a row exceed one CTA's shared memory.
+int mg_rmsnorm_matvec_kquant_on_stream(int ggml_type, const uint8_t* w, const float* x, const float* norm_w, float eps, float* y,
+                                       int out_dim, int blocks_per_row, void* stream) {
+    if (out_dim <= 0 || blocks_per_row <= 0 || !w || !x || !norm_w || !y) return (int)cudaErrorInvalidValue;
+    if (ggml_type == 13 && !mg::aligned16(w)) return (int)cudaErrorInvalidValue;
+    if (!limbs_ok(w, out_dim, blocks_per_row)) return (int)cudaErrorInvalidValue;
+    if (ggml_type == 13) return launch_limbs<5, 1>(w, x, nullptr, y, out_dim, blocks_per_row, stream, norm_w, eps);
+    if (ggml_type == 14) return launch_limbs<6, 1>(w, x, nullptr, y, out_dim, blocks_per_row, stream, norm_w, eps);
+    return (int)cudaErrorInvalidValue;
 }
 
 // ggml_type: 12 (Q4_K), 13 (Q5_K) or 14 (Q6_K); d_model a multiple of 256.

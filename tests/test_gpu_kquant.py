@@ -103,6 +103,25 @@ def test_kquant_matvec_with_residual_and_limb_records(orc, cuda, kind, out_dim, 
     assert rel_rms_err(y2.copy_to_host(out_dim), want) <= GEMV_TOL
 
 
+@pytest.mark.parametrize("kind,out_dim,bpr", [(6, 512, 14), (5, 512, 14), (6, 9000, 14), (5, 4099, 2), (6, 300, 40)])
+def test_rmsnorm_fused_in_front_of_kquant_matvec(orc, cuda, kind, out_dim, bpr):
+    """y = W . rms_norm(x): the norm of crates/modgrad-device/src/kfd/llm.rs:921-928 done by every CTA while it
+    converts x, against the oracle's rms_norm followed by its f64 matvec."""
+    rng = np.random.Generator(np.random.PCG64(950 + out_dim + bpr + kind))
+    k = bpr * 256
+    w = synth.kquant_matrix(kind, out_dim, k, rng)
+    x = synth.activations(k, rng) * np.float32(3.0)
+    nw = (1.0 + 0.05 * rng.standard_normal(k, dtype=np.float32)).astype(np.float32)
+    eps = 1e-6
+    wd, xd, nd, yd = upload(w), upload(x), upload(nw), DeviceBuffer(out_dim * 4)
+    assert cuda.mg_rmsnorm_matvec_kquant_on_stream(8 + kind, wd.ptr, xd.ptr, nd.ptr, eps, yd.ptr, out_dim, bpr, None) == 0
+    kern.sync()
+    want = orc.matvec_kquant_f64(kind, w, orc.rms_norm(x, nw, eps), out_dim, bpr)
+    assert rel_rms_err(yd.copy_to_host(out_dim), want) <= 2 * GEMV_TOL   # the norm's own f32 rounding rides on top
+    assert cuda.mg_rmsnorm_matvec_kquant_on_stream(8 + kind, wd.ptr, xd.ptr, None, eps, yd.ptr, out_dim, bpr, None) == 1
+    assert cuda.mg_rmsnorm_matvec_kquant_on_stream(12, wd.ptr, xd.ptr, nd.ptr, eps, yd.ptr, out_dim, bpr, None) == 1
+
+
 def test_q6k_weight_that_is_only_two_byte_aligned(orc, cuda):
     """Q6_K rows are 2-byte aligned; a weight that starts 2 bytes into a word takes the float kernel and refuses records."""
     out_dim, bpr = 300, 14
