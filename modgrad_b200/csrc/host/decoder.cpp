@@ -128,7 +128,8 @@ int fail(mg_decoder* d, int code, const char* what) {
 template <class T>
 int dev_alloc(mg_decoder* d, T** out, size_t count) {
     void* p = nullptr;
-    cudaError_t e = cudaMalloc(&p, count * sizeof(T) ? count * sizeof(T) : 16);
+    const size_t bytes = count * sizeof(T);
+    cudaError_t e = cudaMalloc(&p, bytes != 0 ? bytes : 16);
     if (e != cudaSuccess) return fail(d, (int)e, "cudaMalloc");
     d->allocs.push_back(p);
     *out = static_cast<T*>(p);
