@@ -58,6 +58,21 @@ def test_slices_reassemble():
         assert np.array_equal(np.concatenate(parts), lw[name]), name
 
 
+def test_slices_of_other_k_quants_reassemble():
+    """Row slices are whole rows of blocks whatever the block size (Q5_K 176 bytes, Q6_K 210): the typed engine
+    shards such tensors over the same row ranges."""
+    cfg = dec.DecoderConfig(1, 512, 4, 2, 128, 1024, 64, 8)
+    lw = dec.layer_weights(cfg, 0, 3)
+    rng = np.random.Generator(np.random.PCG64(5))
+    for name, kind in (("wk", 5), ("wv", 6), ("wdown", 6), ("wo", 5)):
+        o, i = cfg.shapes()[name]
+        lw[name] = synth.kquant_matrix(kind, o, i, rng)
+    for name, (o, i) in cfg.shapes().items():
+        parts = [shard.slice_layer(cfg, shard.decoder_shard(cfg, rank, 2), lw)[name] for rank in range(2)]
+        assert np.array_equal(np.concatenate(parts), lw[name]), name
+        assert all(p.size * 2 == lw[name].size for p in parts), name
+
+
 WORKER = r"""
 import os, sys
 import numpy as np, torch, torch.distributed as dist
