@@ -310,8 +310,9 @@ int mg_decoder_create(const mg_decoder_config* cfg, mg_decoder** out);
  * or one of the three.  mg_decoder_upload then expects the byte size of each tensor's type (of this rank's
  * rows); mg_decoder_weight_type reports the type (0 for the f32 norms).  All-default types build the engine of
  * mg_decoder_create[_sharded].  The _sharded form splits rows over the ranks exactly as
- * mg_decoder_create_sharded does; a typed engine gathers with separate peer-store kernels or NCCL (the fused
- * and stamped exchanges belong to the all-Q4_K engine). */
+ * mg_decoder_create_sharded does; a typed engine ends its Q4_K / attention / SwiGLU kernels with the flag-handshake
+ * exchange and puts a peer-store gather kernel behind a Q5_K / Q6_K matvec, or uses NCCL (the stamped exchanges
+ * belong to the all-Q4_K engine). */
 int mg_decoder_create_typed(const mg_decoder_config* cfg, const int* proj_types, int embed_type, int head_type,
                             mg_decoder** out);
 int mg_decoder_create_typed_sharded(const mg_decoder_config* cfg, const int* proj_types, int embed_type, int head_type,

@@ -472,27 +472,33 @@ int norm_project(mg_decoder* d, int n, const uint8_t* const* w, const uint8_t* t
 }
 
 // hidden += W x for one projection whose rows are split over the ranks: one GPU adds in place (the matvec
-// itself adds); a sharded rank writes its rows into `gathered`, the rows are all-gathered and a small
-// kernel adds the whole vector.  x_kind 0: f32 activations, 1: limb records.
+// itself adds); a sharded rank either does the same and ends its kernel with the exchange, or writes its
+// rows into `gathered`, the rows are all-gathered and a small kernel adds the whole vector.
+// x_kind 0: f32 activations, 1: limb records.
 int project_add(mg_decoder* d, int type, const uint8_t* w, const void* x, int x_kind, float* gathered, int site, int cols,
                 const char* what) {
     const int D = d->cfg.d_model;
     const bool sharded = d->world > 1;
-    float* y = sharded ? gathered + (size_t)d->rank * d->d_loc : d->hidden;
-    const float* add = sharded ? nullptr : d->hidden;
+    // a Q4_K matvec can end with the exchange itself (it stores its rows, added in place, into every rank's
+    // hidden state); the other types write a slice that a gather kernel then distributes
+    const bool in_place = !sharded || (d->fused && type == kTypeQ4K);
+    float* mine = d->hidden + (sharded ? (size_t)d->rank * d->d_loc : 0);
+    float* y = in_place ? mine : gathered + (size_t)d->rank * d->d_loc;
+    const float* add = in_place ? mine : nullptr;
     int e;
     if (type == kTypeQ4K) {
         const uint8_t* ws[1] = {w};
         float* ys[1] = {y};
         const float* adds[1] = {add};
         const int rows[1] = {d->d_loc};
+        if (sharded && in_place) mgpeer::set_next_peer_sync(mgpeer::make_sync(d->px, site));
         e = mg_matvec_q4k_multi_on_stream(1, ws, x, x_kind, adds, ys, rows, cols / 256, d->stream);
     } else {
         e = mg_matvec_kquant_on_stream(type, w, x, x_kind, add, y, d->d_loc, cols / 256, d->stream);
     }
     if (e) return fail(d, e, what);
     d->mixed_launches += 1;
-    if (sharded) {
+    if (!in_place) {
         if ((e = gather_equal(d, site, gathered, (size_t)d->d_loc, mgnccl::kFloat32, 4))) return e;
         mg::launch_pdl(residual_add_kernel, dim3((D + 255) / 256), dim3(256), 0, d->stream, d->hidden, (const float*)gathered, D);
         d->mixed_launches += 2;
@@ -502,8 +508,9 @@ int project_add(mg_decoder* d, int type, const uint8_t* w, const void* x, int x_
 
 // One token of an engine whose tensors are not all of the default types: the same arithmetic, queued
 // through the launchers of each tensor's type.  A real checkpoint mixes Q4_K with Q6_K (attn_v, ffn_down,
-// token embedding, LM head) and Q5_K.  Row-sharded, the four exchanges of a layer are separate gathers
-// (peer-store gather kernels, or NCCL), not fused into the producing kernels.
+// token embedding, LM head) and Q5_K.  Row-sharded, the exchanges of a layer are fused into the producing
+// kernels that can do it (attention, Q4_K matvecs, SwiGLU: flag handshake at their end) and are a peer-store
+// gather kernel with the same handshake behind a Q5_K / Q6_K matvec; or all of them NCCL.
 int queue_token_mixed(mg_decoder* d) {
     const mg_decoder_config& c = d->cfg;
     void* s = d->stream;
@@ -532,13 +539,14 @@ int queue_token_mixed(mg_decoder* d) {
             const int rows[3] = {q_loc, kv_loc, kv_loc};
             if ((e = norm_project(d, 3, w, L.type, L.attn_norm, y, rows, D, "qkv"))) return e;
         }
-        // this rank's heads land at their place in the full attention vector
+        // this rank's heads land at their place in the full attention vector (and, fused, in every peer's)
+        if (d->fused) mgpeer::set_next_peer_sync(mgpeer::make_sync(d->px, kSiteHeads));
         if ((e = mg_sdpa_rope_decode_f16kv_on_stream(d->q, d->k, d->v, L.k_cache, L.v_cache, d->att_full + (size_t)d->h0 * hd, Hl,
                                                      KVl, hd, 0, pos_dev, scale, c.rope_base, d->rope_freq, d->attn_scratch,
                                                      d->n_splits, s)))
             return fail(d, e, "attention");
         d->mixed_launches += 1;
-        if ((e = gather_heads(d))) return e;
+        if (!d->fused && (e = gather_heads(d))) return e;
         if ((e = project_add(d, L.type[3], L.wo, d->att_full, 0, d->tmp_full, kSiteOut, q_dim, "o_proj"))) return e;
         {
             const uint8_t* w[2] = {L.wgate, L.wup};
@@ -550,9 +558,12 @@ int queue_token_mixed(mg_decoder* d) {
             // SwiGLU straight into limb records (a rank's slice is a whole number of records), which the Q4_K,
             // Q5_K and Q6_K down projections all read
             uint8_t* rec = static_cast<uint8_t*>(d->records) + mg_q4k_limb_record_bytes(d->f_loc) * d->rank;
+            if (d->fused) mgpeer::set_next_peer_sync(mgpeer::make_sync(d->px, kSiteRecords));
             if ((e = mg_swiglu_limbs_on_stream(d->gate, d->up, nullptr, d->f_loc, rec, s))) return fail(d, e, "swiglu");
             d->mixed_launches += 1;
-            if ((e = gather_equal(d, kSiteRecords, d->records, mg_q4k_limb_record_bytes(d->f_loc), mgnccl::kUint8, 1))) return e;
+            if (!d->fused &&
+                (e = gather_equal(d, kSiteRecords, d->records, mg_q4k_limb_record_bytes(d->f_loc), mgnccl::kUint8, 1)))
+                return e;
             if ((e = project_add(d, L.type[6], L.wdown, d->records, 1, d->tmp_down, kSiteDown, F, "down"))) return e;
         } else {   // one GPU only (refused at creation otherwise)
             if ((e = launch_swiglu_on_stream(d->gate, d->up, d->gate, F, s))) return fail(d, e, "swiglu");
@@ -580,8 +591,9 @@ int queue_token_mixed(mg_decoder* d) {
         if ((e = mg_argmax_on_stream(d->logits, d->v_loc, local_tok, d->argmax_scratch, nullptr, nullptr, s)))
             return fail(d, e, "argmax");
         mg::launch_pdl(local_pair_kernel, dim3(1), dim3(1), 0, d->stream, (const float*)d->logits, (const int*)local_tok,
-                       d->rank * d->v_loc, d->pair_buf + 2 * d->rank, mgpeer::PeerSync{});
-        if ((e = gather_equal(d, kSitePairs, d->pair_buf, 2, mgnccl::kFloat32, 4))) return e;
+                       d->rank * d->v_loc, d->pair_buf + 2 * d->rank,
+                       d->fused ? mgpeer::make_sync(d->px, kSitePairs) : mgpeer::PeerSync{});
+        if (!d->fused && (e = gather_equal(d, kSitePairs, d->pair_buf, 2, mgnccl::kFloat32, 4))) return e;
         mg::launch_pdl(argmax_pairs_kernel, dim3(1), dim3(1), 0, d->stream, (const float*)d->pair_buf, d->world, tok_dev, d->history,
                        (const int*)step_dev);
         d->mixed_launches += 2;
@@ -869,7 +881,9 @@ int create_impl(const mg_decoder_config* cfg, int rank, int world, const void* n
     int init[4] = {0, 1, 0, 0};
     if ((e = cudaMemcpy(d->state, init, sizeof init, cudaMemcpyHostToDevice)) != cudaSuccess) return bail((int)e);
     if (world > 1 && (rc = setup_peer_exchange(d))) return bail(rc);
-    if (d->mixed) d->fused = d->stamped = false;  // the typed path gathers with separate kernels (or NCCL)
+    // the typed path ends its Q4_K / attention / SwiGLU kernels with the handshake exchange and gathers behind
+    // the other types with a kernel using the same handshake; its consumers read plain arrays, not stamped words
+    if (d->mixed) d->stamped = false;
     *out = d;
     return 0;
 }
@@ -888,7 +902,7 @@ int mg_decoder_create_sharded(const mg_decoder_config* cfg, int rank, int world,
 // Q4_K (12), Q5_K (13) or Q6_K (14); the token embedding and the LM head F16 (1) or one of the three.
 // proj_types holds n_layers * 7 ids in the order q, k, v, o, gate, up, down.  An engine whose types are
 // all the defaults is the one mg_decoder_create_sharded builds.  Row-sharded like that one (same row
-// ranges, same uploads), with the exchanges as separate gathers.
+// ranges, same uploads); see queue_token_mixed for its exchanges.
 int mg_decoder_create_typed_sharded(const mg_decoder_config* cfg, const int* proj_types, int embed_type, int head_type,
                                     int rank, int world, const void* nccl_id128, mg_decoder** out) {
     if (!cfg || !proj_types || !out) return (int)cudaErrorInvalidValue;

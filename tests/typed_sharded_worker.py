@@ -53,7 +53,8 @@ def main():
         assert not bad, bad
     modes = [None] * world
     dist.all_gather_object(modes, d.gather_mode())
-    want_mode = "nccl" if os.environ.get("MODGRAD_DECODER_GATHER") == "nccl" else "peer"
+    # the typed engine has no stamped exchanges: it fuses with the flag handshake unless asked for less
+    want_mode = {"nccl": "nccl", "peer": "peer"}.get(os.environ.get("MODGRAD_DECODER_GATHER", ""), "fused")
     assert all(m == want_mode for m in modes), modes
     d.set_position(0)
     toks, ms = d.generate(3, 8)
