@@ -220,6 +220,85 @@ static void forward_token_impl(const orc_decoder_cfg* cfg, const orc_decoder_lay
     free(hidden); free(cur); free(q); free(k); free(v); free(att); free(tmp); free(gate); free(up);
 }
 
+/* ---- tensors of mixed types -----------------------------------------------------------------------
+ * The reference's matvec dispatches on the tensor's GGML type (llm.rs:498-533: Q4_K fused dot, Q6_K its own
+ * dot, every other quant dequantise-then-f64-dot) and its embedding lookup dequantises one row of a quantised
+ * table (embed_token, llm.rs:898-918).  orc_forward_token_typed is forward_token (llm.rs:1177-1298) over such
+ * tensors: type ids are GGML's (1 F16, 12 Q4_K, 13 Q5_K, 14 Q6_K); matvecs accumulate in f64 and round once,
+ * as the f64 arms of the reference do. */
+void orc_dequantize_row_q4_k(const uint8_t* data, float* out, size_t n_blocks);
+void orc_dequantize_row_q5_k(const uint8_t* data, float* out, size_t n_blocks);
+void orc_dequantize_row_q6_k(const uint8_t* data, float* out, size_t n_blocks);
+void orc_matvec_kquant_f64(int kind, const uint8_t* w, const float* x, double* y, int out_dim, int bpr);
+
+typedef struct {
+    const void* w[7];   /* wq, wk, wv, wo, wgate, wup, wdown */
+    int type[7];
+    const float *attn_norm, *ffn_norm;
+    uint16_t *k_cache, *v_cache; /* [max_seq][n_kv_heads*head_dim] half */
+} orc_typed_layer;
+
+static void typed_matvec(int type, const void* w, const float* x, float* y, int out_dim, int in_dim) {
+    if (type == 12) { orc_matvec_q4k((const uint8_t*)w, x, y, out_dim, in_dim / 256, 2 /* f64 */, 0); return; }
+    if (type == 1) { orc_matvec_f16((const uint16_t*)w, x, y, out_dim, in_dim); return; }
+    double* t = (double*)malloc(sizeof(double) * (size_t)out_dim);
+    orc_matvec_kquant_f64(type == 13 ? 5 : 6, (const uint8_t*)w, x, t, out_dim, in_dim / 256);
+    for (int i = 0; i < out_dim; ++i) y[i] = (float)t[i];
+    free(t);
+}
+
+void orc_forward_token_typed(const orc_decoder_cfg* cfg, const orc_typed_layer* layers, const void* embed, int embed_type,
+                             const void* lm_head, int head_type, const float* out_norm_w, int pos, uint32_t token,
+                             float* logits) {
+    int D = cfg->d_model, H = cfg->n_heads, KVH = cfg->n_kv_heads, hd = cfg->head_dim;
+    int q_dim = H * hd, kv_dim = KVH * hd, F = cfg->d_ff;
+    float* hidden = (float*)malloc(sizeof(float) * D);
+    float* cur = (float*)malloc(sizeof(float) * D);
+    float* q = (float*)malloc(sizeof(float) * q_dim);
+    float* k = (float*)malloc(sizeof(float) * kv_dim);
+    float* v = (float*)malloc(sizeof(float) * kv_dim);
+    float* att = (float*)malloc(sizeof(float) * q_dim);
+    float* tmp = (float*)malloc(sizeof(float) * D);
+    float* gate = (float*)malloc(sizeof(float) * F);
+    float* up = (float*)malloc(sizeof(float) * F);
+
+    if (embed_type == 1) {
+        const uint16_t* e = (const uint16_t*)embed;
+        for (int i = 0; i < D; ++i) hidden[i] = orc_f16_to_f32(e[(size_t)token * D + i]);
+    } else {
+        size_t bb = embed_type == 12 ? 144 : embed_type == 13 ? 176 : 210;
+        const uint8_t* row = (const uint8_t*)embed + (size_t)token * (D / 256) * bb;
+        if (embed_type == 12) orc_dequantize_row_q4_k(row, hidden, D / 256);
+        else if (embed_type == 13) orc_dequantize_row_q5_k(row, hidden, D / 256);
+        else orc_dequantize_row_q6_k(row, hidden, D / 256);
+    }
+    for (int l = 0; l < cfg->n_layers; ++l) {
+        const orc_typed_layer* L = &layers[l];
+        orc_rms_norm(hidden, L->attn_norm, cur, D, cfg->rms_eps);
+        typed_matvec(L->type[0], L->w[0], cur, q, q_dim, D);
+        typed_matvec(L->type[1], L->w[1], cur, k, kv_dim, D);
+        typed_matvec(L->type[2], L->w[2], cur, v, kv_dim, D);
+        orc_apply_rope(q, pos, H, hd, cfg->rope_base);
+        orc_apply_rope(k, pos, KVH, hd, cfg->rope_base);
+        for (int i = 0; i < kv_dim; ++i) {
+            L->k_cache[(size_t)pos * kv_dim + i] = orc_f32_to_f16_rne(k[i]);
+            L->v_cache[(size_t)pos * kv_dim + i] = orc_f32_to_f16_rne(v[i]);
+        }
+        orc_attention_f16kv(q, L->k_cache, L->v_cache, att, pos + 1, H, KVH, hd);
+        typed_matvec(L->type[3], L->w[3], att, tmp, D, q_dim);
+        for (int i = 0; i < D; ++i) hidden[i] += tmp[i];
+        orc_rms_norm(hidden, L->ffn_norm, cur, D, cfg->rms_eps);
+        typed_matvec(L->type[4], L->w[4], cur, gate, F, D);
+        typed_matvec(L->type[5], L->w[5], cur, up, F, D);
+        orc_swiglu_inplace(gate, up, F);
+        typed_matvec(L->type[6], L->w[6], gate, tmp, D, F);
+        for (int i = 0; i < D; ++i) hidden[i] += tmp[i];
+    }
+    orc_rms_norm(hidden, out_norm_w, cur, D, cfg->rms_eps);
+    typed_matvec(head_type, lm_head, cur, logits, cfg->vocab, D);
+    free(hidden); free(cur); free(q); free(k); free(v); free(att); free(tmp); free(gate); free(up);
+}
+
 /* Half-precision KV cache: the 7B-class configuration this build benchmarks. */
 void orc_forward_token(const orc_decoder_cfg* cfg, const orc_decoder_layer* layers,
                        const uint16_t* embed, const uint16_t* lm_head, const float* out_norm_w,

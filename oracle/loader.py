@@ -38,6 +38,13 @@ class DecoderLayer(C.Structure):
                                           "attn_norm", "ffn_norm", "k_cache", "v_cache")]
 
 
+class TypedLayer(C.Structure):
+    """orc_typed_layer: seven weight pointers (wq, wk, wv, wo, wgate, wup, wdown), their GGML type ids,
+    the two norm vectors and the half KV caches."""
+    _fields_ = [("w", C.c_void_p * 7), ("type", C.c_int * 7), ("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p),
+                ("k_cache", C.c_void_p), ("v_cache", C.c_void_p)]
+
+
 def _p(a: np.ndarray):
     return a.ctypes.data_as(C.c_void_p)
 
@@ -75,6 +82,9 @@ class OracleLib:
         c.orc_argmax.restype = C.c_uint32
         c.orc_argmax.argtypes = [C.c_void_p, C.c_int]
         c.orc_forward_token.argtypes = [C.c_void_p] * 5 + [C.c_int, C.c_uint32, C.c_void_p, C.c_int]
+        c.orc_forward_token_typed.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
+                                              C.c_int, C.c_uint32, C.c_void_p]
+        c.orc_forward_token_typed.restype = None
         c.orc_forward_token_f32kv.argtypes = [C.c_void_p] * 7 + [C.c_int, C.c_uint32, C.c_void_p, C.c_int]
 
     # ---- format -----------------------------------------------------------------------
@@ -202,6 +212,16 @@ class OracleLib:
         logits = np.empty(cfg.vocab, dtype=np.float32)
         self.c.orc_forward_token(C.byref(cfg), arr, _p(embed), _p(lm_head), _p(out_norm), pos, token,
                                  _p(logits), mode)
+        return logits
+
+    def forward_token_typed(self, cfg: DecoderCfg, layers, embed, embed_type, lm_head, head_type, out_norm, pos,
+                            token) -> np.ndarray:
+        """forward_token over tensors of mixed GGML types (layers: TypedLayer records; type ids 1 F16, 12 Q4_K,
+        13 Q5_K, 14 Q6_K), f64-accumulated matvecs, half KV caches appended in place."""
+        arr = (TypedLayer * len(layers))(*layers)
+        logits = np.empty(cfg.vocab, dtype=np.float32)
+        self.c.orc_forward_token_typed(C.byref(cfg), arr, _p(embed), int(embed_type), _p(lm_head), int(head_type),
+                                       _p(out_norm), pos, token, _p(logits))
         return logits
 
     def forward_token_f32kv(self, cfg: DecoderCfg, layers, k32, v32, embed, lm_head, out_norm, pos, token,
